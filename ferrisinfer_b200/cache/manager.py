@@ -10,13 +10,13 @@ last sample, RNG state) lives in the session (crates/ferrisinfer-runtime/src/ses
 Here ONE manager serves all requests:
 
 * Mixers that keep keys and values declare a ``PagedKV`` need.  Run-order entries with the same
-  need (kv heads, head size, window) form a **page group**: the group has one pool of page ids and
+  need (kv heads, head size, window or chunk) form a **page group**: the group has one pool of page ids and
   one block table per request, and each entry of the group has key and value tensors of its own
   ``[pages, kv heads, page size, head dim]`` addressed by the group's page ids.  Groups with
   different needs (all keys / a window of them) have pools and tables of their own.
 * A request's pages are allocated before a step for every token the step brings (``extend``),
   counted as held after it (``commit``), and given back when the request ends (``release``) or, in a
-  window group, as soon as the window has passed them (in ``commit``); a page that is given back is
+  window group (or one of chunks), as soon as the window has passed them or their chunk is over (in ``commit``); a page that is given back is
   the next one handed out.
 * Mixers with a ``FixedState`` need, and the engine itself (sampler state), get a tensor
   ``[slots, *shape]``; a request holds one slot id from admission to release, and the slot's rows
@@ -57,6 +57,16 @@ class PageGroup:
     @property
     def window(self) -> Optional[int]:
         return self.need.window
+
+    @property
+    def keeps_all(self) -> bool:
+        """No window and no chunks: every page stays until the request ends."""
+        return self.need.keeps_all
+
+    @property
+    def span(self) -> Optional[int]:
+        """The most keys a token reads (None: all of them)."""
+        return self.need.window if self.need.window is not None else self.need.chunk
 
 
 @dataclass
@@ -198,7 +208,7 @@ class CacheManager:
         self.requests: dict = {}
         # Pages of prompts are shared only where a page means the same for every layer: all page groups keep
         # every key (no window) and no mixer keeps a state of its own.
-        shareable = bool(self.groups) and all(g.window is None for g in self.groups) and not any(
+        shareable = bool(self.groups) and all(g.keeps_all for g in self.groups) and not any(
             isinstance(leaf, FixedState) for n in needs for leaf in leaf_needs(n))
         self.prefix = PrefixIndex() if (prefix_sharing and shareable) else None
         self.min_prefix_share_tokens = int(min_prefix_share_tokens)
@@ -319,9 +329,7 @@ class CacheManager:
     # --------------------------------------------------------------------- pages
     def _first_needed_block(self, g: PageGroup, num_tokens: int) -> int:
         """Lowest block that a query at position >= num_tokens can still read."""
-        if g.window is None:
-            return 0
-        return max(0, num_tokens - g.window + 1) // self.page_size
+        return g.need.first_needed(num_tokens) // self.page_size
 
     def pages_needed(self, request_id, new_total: int) -> dict:
         """gid -> pages that ``extend(request_id, new_total)`` would take from the pool."""
@@ -425,7 +433,7 @@ class CacheManager:
                 rc.registered_blocks += 1
         freed = 0
         for g in self.groups:
-            if g.window is None:
+            if g.keeps_all:
                 continue
             table = rc.tables[g.gid]
             upto = min(self._first_needed_block(g, new_total), len(table))

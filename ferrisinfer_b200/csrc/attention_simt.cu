@@ -4,7 +4,8 @@
 // a running maximum, sum and weighted value sum each, merged at the end.
 //
 //   query head hq uses kv head hq / (nh / nkv); s_j = (q . k_j) * scale; the query at absolute
-//   position P attends keys lo..P, lo = 0 or P - window + 1; softmax over them; out = sum w_j v_j.
+//   position P attends keys lo..P, lo = 0, P - window + 1 or (a negative `window`: a chunk of that many positions)
+//   the start of P's chunk; softmax over them; out = sum w_j v_j.
 //   With `slopes` (one per query head; a position encoding that acts on the scores, not on q and k):
 //   s_j += slopes[hq] * (j - P), a penalty linear in the distance.
 // (crates/ferrisinfer-kernel/src/cpu/attention.rs:729-781, 1125-1155: streaming softmax with a
@@ -49,6 +50,13 @@ __device__ __forceinline__ float with_terms(float s, const HeadTerms& t, int j, 
     if (t.kind == 2) return s - t.a * log1pf(t.b * (float)(P - j));
     return s;
 }
+// The first key that the query at position P sees.  window > 0: the last `window` keys, itself included; window < 0:
+// the keys of its own chunk, positions being counted off in chunks of -window from 0; 0: every key.
+__device__ __forceinline__ int first_key(int P, int window) {
+    if (window > 0) return P - window + 1 > 0 ? P - window + 1 : 0;
+    if (window < 0) return P - P % (-window);
+    return 0;
+}
 // the sink's share of the denominator, relative to the maximum mm of the keys' scores
 __device__ __forceinline__ float sink_share(const ScoreTerms& st, int h, float mm) { return st.sink ? expf(st.sink[h] - mm) : 0.0f; }
 
@@ -67,7 +75,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
     const int hk = hq / (nh / nkv);
     const int seq = token_seq[t];
     const int P = positions[t];
-    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int lo = first_key(P, window);
     const int* table = block_tables + (size_t)seq * max_blocks;
     const HeadTerms ht = head_terms(st, hq);
     const size_t vs = st.v_stride ? st.v_stride : dv;
@@ -222,7 +230,7 @@ __global__ void __launch_bounds__(AL_THREADS)
     const int hk = hq / (nh / nkv);
     const int seq = token_seq[t];
     const int P = positions[t];
-    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int lo = first_key(P, window);
     const int* table = block_tables + (size_t)seq * max_blocks;
     const HeadTerms ht = head_terms(st, hq);
     const size_t vs = st.v_stride ? st.v_stride : dv;
@@ -339,7 +347,7 @@ __global__ void __launch_bounds__(AG_THREADS)
     const int hk = h0 / (nh / nkv);
     const int seq = token_seq[t];
     const int P = positions[t];
-    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int lo = first_key(P, window);
     const int* table = block_tables + (size_t)seq * max_blocks;
     const int ch = d >> 4, cv = dv >> 4;
     const size_t vs = st.v_stride ? st.v_stride : dv;
@@ -615,7 +623,7 @@ __global__ void __launch_bounds__(TL_THREADS)
         int tb = ta;  // its last token within the tile
         while (tb + 1 < t_end && token_seq[tb + 1] == sq) ++tb;
         const int pa = positions[ta], pb = positions[tb];
-        const int kmin = (window > 0 && pa - window + 1 > 0) ? pa - window + 1 : 0;
+        const int kmin = first_key(pa, window);  // of the first token: no later token of the request sees an earlier key
         const int* table = block_tables + (size_t)sq * max_blocks;
         for (int j0 = kmin & ~(TL_KEYS - 1); j0 <= pb; j0 += TL_KEYS) {
             __syncthreads();  // the tile before has been used (and, the first time, the queries are in place)
@@ -657,7 +665,7 @@ __global__ void __launch_bounds__(TL_THREADS)
             float alpha[2];
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
-                const int lo = (window > 0 && rpos[a] - window + 1 > 0) ? rpos[a] - window + 1 : 0;
+                const int lo = first_key(rpos[a], window);
                 float best = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {

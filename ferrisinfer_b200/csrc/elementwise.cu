@@ -647,3 +647,92 @@ FERRIS_API int ferris_qk_prepare_cache_write(void* qkv, int ld, int dtype, const
         FERRIS_REFUSE("qk_prepare: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Dynamic tanh, a norm without statistics: out[r, i] = tanh(alpha * x[src(r), i]) * w[i] + b[i], alpha one learned
+// number (read from the device).  fp32 arithmetic, tanhf in full precision; the output in the activations' type.
+// Rows of a multiple of four elements go 16 bytes a thread.
+// ---------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void __launch_bounds__(256) dynamic_tanh_kernel(const float* x, const float* __restrict__ w,
+                                                           const float* __restrict__ b, const float* __restrict__ alpha,
+                                                           const int* __restrict__ row_index, TOut* __restrict__ out,
+                                                           int rows, int hidden) {
+    const float a = alpha[0];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t n = (size_t)rows * hidden;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / hidden;
+        const int i = (int)(e % hidden);
+        const size_t src = row_index ? (size_t)row_index[r] : r;
+        out[e] = from_float<TOut>(fmaf(tanhf(a * x[src * hidden + i]), w[i], b[i]));
+    }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256) dynamic_tanh_vec_kernel(const float* x, const float* __restrict__ w,
+                                                               const float* __restrict__ b,
+                                                               const float* __restrict__ alpha,
+                                                               const int* __restrict__ row_index, TOut* __restrict__ out,
+                                                               int rows, int hidden) {
+    const float a = alpha[0];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n4 = hidden >> 2;
+    const size_t n = (size_t)rows * n4;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / n4;
+        const int i = (int)(e % n4);
+        const size_t src = row_index ? (size_t)row_index[r] : r;
+        const float4 v = reinterpret_cast<const float4*>(x + src * hidden)[i];
+        const float4 g = w4[i], c = b4[i];
+        store4(out + r * hidden + 4 * i, fmaf(tanhf(a * v.x), g.x, c.x), fmaf(tanhf(a * v.y), g.y, c.y),
+               fmaf(tanhf(a * v.z), g.z, c.z), fmaf(tanhf(a * v.w), g.w, c.w));
+    }
+}
+
+FERRIS_API int ferris_dynamic_tanh(const float* x, const float* w, const float* b, const float* alpha,
+                                   const int* row_index, void* out, int out_dtype, int rows, int hidden, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (hidden <= 0 || !w || !b || !alpha) FERRIS_REFUSE("dynamic tanh: hidden=%d, or a tensor is missing", hidden);
+    if (out_dtype != FERRIS_F32 && out_dtype != FERRIS_BF16) FERRIS_REFUSE("dynamic tanh: unknown dtype %d", out_dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = hidden % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out) & 15) == 0;
+    const size_t n = (size_t)rows * (vec ? hidden / 4 : hidden);
+    const size_t want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16)), block(256);
+    if (vec) {
+        if (out_dtype == FERRIS_F32)
+            ferris_launch(dynamic_tanh_vec_kernel<float>, grid, block, 0, s, x, w, b, alpha, row_index, (float*)out, rows, hidden);
+        else
+            ferris_launch(dynamic_tanh_vec_kernel<bf16>, grid, block, 0, s, x, w, b, alpha, row_index, (bf16*)out, rows, hidden);
+    } else {
+        if (out_dtype == FERRIS_F32)
+            ferris_launch(dynamic_tanh_kernel<float>, grid, block, 0, s, x, w, b, alpha, row_index, (float*)out, rows, hidden);
+        else
+            ferris_launch(dynamic_tanh_kernel<bf16>, grid, block, 0, s, x, w, b, alpha, row_index, (bf16*)out, rows, hidden);
+    }
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Soft cap of logits, in place: z <- cap * tanh(z / cap).  fp32.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) softcap_kernel(float* z, long long n, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x)
+        z[e] = cap * tanhf(z[e] / cap);
+}
+
+FERRIS_API int ferris_softcap(float* z, long long n, float cap, void* stream) {
+    if (n <= 0) return FERRIS_OK;
+    if (!(cap > 0.0f)) FERRIS_REFUSE("softcap: the cap must be positive, found %g", (double)cap);
+    const long long want = (n + 255) / 256;
+    ferris_launch(softcap_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, (cudaStream_t)stream,
+                  z, n, cap);
+    FERRIS_LAUNCH_CHECK();
+}

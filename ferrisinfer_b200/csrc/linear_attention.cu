@@ -11,7 +11,8 @@
 // memory, activation applied once, and then each walks those tokens alone.  A step of single tokens and a portion
 // of a prompt are the same loop, and a long portion is cut into segments that run side by side (see the kernel).  The state lies
 // transposed in memory, [slot, head, vdim, dim], so that a warp reads and writes whole rows of it.
-// q, k, v may be passed through SiLU on the way in (`silu`), in fp32 whatever the storage type.
+// q, k, v may be passed through SiLU on the way in (`silu`), in fp32 whatever the storage type; q and k may be
+// rotated by their positions there, and k scaled (RotaryArgs): what enters the recurrence is then fp32 throughout.
 #include <math.h>
 
 #include "common.cuh"
@@ -24,6 +25,17 @@ constexpr int LA_STAGE = 8;      // tokens whose q, k, v stand in shared memory 
 constexpr int LA_MAX_DIM = 256;  // largest head size
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// Rotary positions on q and k on their way in (positions null: none), and a factor on k after them.  The first
+// `rotary` elements of a head are rotated by the token's position: the pair (u, v), elements (i, i + rotary / 2)
+// or, `interleaved`, (2i, 2i + 1), becomes (u c - v s, v c + u s) with c = mag cos(pos * freq[i]), s = mag sin(same);
+// position x frequency is one fp32 product, sine and cosine are in full precision.
+struct RotaryArgs {
+    const int* positions;
+    const float* freq;
+    int rotary, interleaved;
+    float mag, k_scale;
+};
 
 // Eight sums over the warp's lanes with nine shuffles instead of forty: at each of the first three steps a lane
 // hands half of its partial sums to its partner and keeps the other half.  Every lane returns the sum of column
@@ -60,7 +72,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
     const T* qkv, int ld, int q_off, int k_off, int v_off, float* __restrict__ out, int ldo, float* state,
     float* scratch, const float* __restrict__ decay, const int* __restrict__ seq_q_start,
     const int* __restrict__ seq_state_slot, int heads, int dim, int vdim, int silu, int write_state, int seg_len,
-    int segs_max) {
+    int segs_max, const RotaryArgs rot) {
     pdl_wait();
     pdl_launch_dependents();
     // q, k and this block's 32 columns of v of LA_STAGE tokens at a time, activation applied once, for all four warps
@@ -116,6 +128,26 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attention_scan_kernel(
             for (int e = lane; e < bcols; e += 32) {
                 const float a = to_float(row[v_off + h * vdim + bcol0 + e]);
                 stage[tt][2 * LA_MAX_DIM + e] = silu ? silu_f(a) : a;
+            }
+            if (rot.positions || rot.k_scale != 1.0f) {
+                __syncwarp();
+                const int rotary = rot.positions ? rot.rotary : 0, half = rotary >> 1;
+                const float p = rot.positions ? (float)rot.positions[t0 + tt] : 0.0f;
+                for (int f = lane; f < half; f += 32) {
+                    float sn, cs;
+                    sincosf(p * rot.freq[f], &sn, &cs);
+                    sn *= rot.mag, cs *= rot.mag;
+                    const int iu = rot.interleaved ? 2 * f : f, iv = rot.interleaved ? 2 * f + 1 : f + half;
+                    const float ku = stage[tt][iu], kv = stage[tt][iv];
+                    stage[tt][iu] = (ku * cs - kv * sn) * rot.k_scale;
+                    stage[tt][iv] = (kv * cs + ku * sn) * rot.k_scale;
+                    if (MODE != 1) {
+                        const float qu = stage[tt][LA_MAX_DIM + iu], qv = stage[tt][LA_MAX_DIM + iv];
+                        stage[tt][LA_MAX_DIM + iu] = qu * cs - qv * sn;
+                        stage[tt][LA_MAX_DIM + iv] = qv * cs + qu * sn;
+                    }
+                }
+                for (int e = rotary + lane; e < dim; e += 32) stage[tt][e] *= rot.k_scale;
             }
         }
         __syncthreads();
@@ -215,13 +247,14 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const float* o, int 
 template <typename T, int MODE>
 void launch_scan_mode(const void* qkv, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
                       float* scratch, const float* decay, const int* seq_q_start, const int* seq_state_slot, int seqs,
-                      int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, cudaStream_t s) {
+                      int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, const RotaryArgs rot,
+                      cudaStream_t s) {
     const dim3 grid(MODE == 0 ? seqs : seqs * segs_max, heads, (vdim + LA_COLS * LA_WARPS - 1) / (LA_COLS * LA_WARPS));
     const dim3 block(LA_WARPS * 32);
 #define FERRIS_LA_LAUNCH(RPL)                                                                                       \
     ferris_launch(linear_attention_scan_kernel<T, RPL, MODE>, grid, block, 0, s, (const T*)qkv, ld, q_off, k_off,   \
                   v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, heads, dim, vdim, silu,       \
-                  write_state, seg_len, segs_max)
+                  write_state, seg_len, segs_max, rot)
     if (dim <= 32)
         FERRIS_LA_LAUNCH(1);
     else if (dim <= 64)
@@ -236,19 +269,20 @@ void launch_scan_mode(const void* qkv, int ld, int q_off, int k_off, int v_off, 
 template <typename T>
 int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float* out, int ldo, float* state,
                 float* scratch, const float* decay, const int* seq_q_start, const int* seq_state_slot, int seqs,
-                int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, cudaStream_t s) {
+                int heads, int dim, int vdim, int silu, int write_state, int seg_len, int segs_max, const RotaryArgs rot,
+                cudaStream_t s) {
     if (segs_max <= 1) {
         launch_scan_mode<T, 0>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot,
-                               seqs, heads, dim, vdim, silu, write_state, seg_len, 1, s);
+                               seqs, heads, dim, vdim, silu, write_state, seg_len, 1, rot, s);
         FERRIS_LAUNCH_CHECK();
     }
     launch_scan_mode<T, 1>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs,
-                           heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
+                           heads, dim, vdim, silu, write_state, seg_len, segs_max, rot, s);
     const size_t per_state = (size_t)heads * vdim * dim;
     ferris_launch(linear_attention_combine_kernel, dim3((unsigned)((per_state + 255) / 256), seqs), dim3(256), 0, s,
                   (const float*)state, scratch, decay, seq_q_start, seq_state_slot, heads, dim, vdim, seg_len);
     launch_scan_mode<T, 2>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs,
-                           heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
+                           heads, dim, vdim, silu, write_state, seg_len, segs_max, rot, s);
     FERRIS_LAUNCH_CHECK();
 }
 
@@ -262,8 +296,13 @@ int launch_scan(const void* qkv, int ld, int q_off, int k_off, int v_off, float*
 FERRIS_API int ferris_linear_attention(const void* qkv, int ld, int q_off, int k_off, int v_off, int dtype, float* out,
                                        int ldo, float* state, const float* decay, const int* seq_q_start,
                                        const int* seq_state_slot, int seqs, int heads, int dim, int vdim, int silu,
-                                       int write_state, int seg_len, int segs_max, float* scratch, void* stream) {
+                                       int write_state, int seg_len, int segs_max, float* scratch,
+                                       const int* positions, const float* freq, int rotary, int interleaved, float mag,
+                                       float k_scale, void* stream) {
     if (seqs <= 0) return FERRIS_OK;
+    if (positions && (rotary < 0 || rotary > dim || (rotary & 1) || (rotary > 0 && !freq)))
+        FERRIS_REFUSE("linear attention: %d rotated elements of heads of %d", rotary, dim);
+    const RotaryArgs rot = {positions, freq, rotary, interleaved, mag, k_scale};
     if (segs_max > 1 && (!scratch || seg_len <= 0)) FERRIS_REFUSE("linear attention: segments need scratch and a length");
     if (seqs > 65535) FERRIS_REFUSE("linear attention: %d requests are more than one launch takes", seqs);
     if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 256) FERRIS_REFUSE("linear attention: heads=%d dim=%d vdim=%d (dim at most 256)", heads, dim, vdim);
@@ -271,9 +310,9 @@ FERRIS_API int ferris_linear_attention(const void* qkv, int ld, int q_off, int k
     if (!state || !decay) FERRIS_REFUSE("linear attention: no state or no decay");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        return launch_scan<float>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
+        return launch_scan<float>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, rot, s);
     if (dtype == FERRIS_BF16)
-        return launch_scan<bf16>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, s);
+        return launch_scan<bf16>(qkv, ld, q_off, k_off, v_off, out, ldo, state, scratch, decay, seq_q_start, seq_state_slot, seqs, heads, dim, vdim, silu, write_state, seg_len, segs_max, rot, s);
     FERRIS_REFUSE("linear attention: unknown dtype %d", dtype);
 }
 

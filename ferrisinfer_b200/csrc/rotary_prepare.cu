@@ -1,0 +1,122 @@
+// What stands between the q/k product and attention where queries and keys are normed over their whole projection
+// and then rotated, and where the keys as projected may serve as the values:
+//
+//   q <- q / sqrt(mean(q^2) + eps) * wq      the mean over ALL heads' elements of the token at once (wq spans them)
+//   k <- k / sqrt(mean(k^2) + eps) * wk      likewise; either norm is skipped when its weight is null
+//   values = the third part of the row, or (values_from_keys) k as projected, before the norm
+//   the first R elements of every q and k head rotated by the token's position: the pair (u, v), elements
+//   (i, i + R/2) of a head ("half") or (2i, 2i + 1) ("interleaved"), becomes (u c - v s, v c + u s) with
+//   c = mag cos(pos * freq[i]), s = mag sin(pos * freq[i]); the other elements pass
+//   q rewritten in place, k and the values stored into the paged cache.
+//
+// Rows: [nh d | nkv d | nkv dv unless values_from_keys].  Everything is computed in fp32 (position x frequency as one
+// fp32 product, sincosf in full precision); one block per token.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(128) qk_norm_rotary_cache_write_kernel(
+    T* qkv, int ld, const int* __restrict__ positions, const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int nh, int nkv, int d, int dv, int page_size, const float* __restrict__ q_weight,
+    const float* __restrict__ k_weight, float eps, const float* __restrict__ freq, int rotary, int interleaved, float mag,
+    int values_from_keys, int write_kv) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    T* row = qkv + (size_t)t * ld;
+    const int nq = nh * d, nk = nkv * d;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (q_weight) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+            const float v = to_float(row[i]);
+            ss = fmaf(v, v, ss);
+        }
+        inv_q = 1.0f / sqrtf(block_sum(ss, scratch) / (float)nq + eps);
+    }
+    if (k_weight) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+            const float v = to_float(row[nq + i]);
+            ss = fmaf(v, v, ss);
+        }
+        inv_k = 1.0f / sqrtf(block_sum(ss, scratch) / (float)nk + eps);
+    }
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int in_page = slot >= 0 ? slot % page_size : 0;
+    if (slot >= 0) {  // the values first: where they are the keys as projected, before anything touches those
+        const T* vrow = values_from_keys ? row + nq : row + nq + nk;
+        for (int e = threadIdx.x; e < nkv * dv; e += blockDim.x) {
+            const int h = e / dv, i = e % dv;
+            v_cache[(((size_t)page * nkv + h) * page_size + in_page) * dv + i] = vrow[e];
+        }
+    }
+    const int half = rotary >> 1;
+    const int last = slot >= 0 ? nq + nk : nq;  // without a cache to write, the keys are left alone
+    for (int e = threadIdx.x; e < last; e += blockDim.x) {
+        const bool is_q = e < nq;
+        const int h = is_q ? e / d : (e - nq) / d;
+        const int i = is_q ? e % d : (e - nq) % d;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? q_weight : k_weight;
+        const int col = is_q ? e : e - nq;  // the element's place in its projection, where its norm weight lies
+        T* dst = is_q ? row + e - i : k_cache + (((size_t)page * nkv + h) * page_size + in_page) * d;
+        if (i >= rotary) {
+            const float x = to_float(row[e]);
+            dst[i] = from_float<T>(w ? (x * inv) * w[col] : x);
+            continue;
+        }
+        // the first member of a pair works for both
+        int partner, f;
+        if (interleaved) {
+            if (i & 1) continue;
+            partner = 1, f = i >> 1;
+        } else {
+            if (i >= half) continue;
+            partner = half, f = i;
+        }
+        float u = to_float(row[e]), v = to_float(row[e + partner]);
+        if (w) u = (u * inv) * w[col], v = (v * inv) * w[col + partner];
+        float s, c;
+        sincosf((float)pos * freq[f], &s, &c);
+        s *= mag, c *= mag;
+        dst[i] = from_float<T>(u * c - v * s);
+        dst[i + partner] = from_float<T>(v * c + u * s);
+    }
+}
+
+}  // namespace
+
+FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, const int* positions,
+                                                 const int* slot_mapping, void* k_cache, void* v_cache, int tokens, int nh,
+                                                 int nkv, int d, int dv, int page_size, const float* q_weight,
+                                                 const float* k_weight, float eps, const float* freq, int rotary,
+                                                 int interleaved, float mag, int values_from_keys, int write_kv,
+                                                 void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0)
+        FERRIS_REFUSE("qk norm + rotation: nh=%d nkv=%d d=%d dv=%d page_size=%d", nh, nkv, d, dv, page_size);
+    if (rotary < 0 || rotary > d || (rotary & 1) || (rotary > 0 && !freq))
+        FERRIS_REFUSE("qk norm + rotation: %d rotated elements of heads of %d", rotary, d);
+    if (values_from_keys && dv != d) FERRIS_REFUSE("qk norm + rotation: keys of %d cannot serve as values of %d", d, dv);
+    if (ld < (nh + nkv) * d + (values_from_keys ? 0 : nkv * dv)) FERRIS_REFUSE("qk norm + rotation: rows of %d are too short", ld);
+    if (write_kv && (!slot_mapping || !k_cache || !v_cache)) FERRIS_REFUSE("qk norm + rotation: no cache to write");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(qk_norm_rotary_cache_write_kernel<float>, dim3(tokens), dim3(128), 0, s, (float*)qkv, ld, positions,
+                      slot_mapping, (float*)k_cache, (float*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps,
+                      freq, rotary, interleaved, mag, values_from_keys, write_kv);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(qk_norm_rotary_cache_write_kernel<bf16>, dim3(tokens), dim3(128), 0, s, (bf16*)qkv, ld, positions,
+                      slot_mapping, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps,
+                      freq, rotary, interleaved, mag, values_from_keys, write_kv);
+    else
+        FERRIS_REFUSE("qk norm + rotation: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}

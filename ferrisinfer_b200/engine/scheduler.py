@@ -158,7 +158,7 @@ class Scheduler:
         most = min(len(prompt) + budget, cfg.max_sequence_length)
         ps = self.cache.page_size
         for g in self.cache.groups:
-            window = g.window
+            window = g.span  # the most keys a token reads: a window, a chunk, or None for all
             span = most if window is None else min(most, window + 2 * ps)
             if -(-span // ps) > g.pool.num_pages:
                 raise SchedulerError(

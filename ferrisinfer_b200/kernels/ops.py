@@ -717,8 +717,11 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                          score_slopes=None, v_head_dim: Optional[int] = None,
-                         max_q_len: int = 1, max_kv_len: int = 0, workspace=None, values_in_keys: bool = False):
+                         max_q_len: int = 1, max_kv_len: int = 0, workspace=None, values_in_keys: bool = False,
+                         chunk: int = 0):
     """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
+    ``window``: the query at position P sees the keys P - window + 1 .. P (0: all).  ``chunk`` (instead of a window):
+    positions are counted off in chunks of that many from 0, and a query sees the keys of its own chunk up to itself.
     ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
     slopes[head] * (j - P) added; or a ``ScoreTerms`` (slopes, a logarithmic distance penalty, a sink in the softmax's
     denominator).  ``v_head_dim``: size of a value head where it differs from the keys'.  ``values_in_keys``: a key's
@@ -728,6 +731,10 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
     tokens): the most keys a request holds, and where scratch comes from; the keys of a token are then cut into
     shares that run side by side, and query heads of one kv head share its keys."""
     dv = int(v_head_dim or head_dim)
+    if chunk:
+        if window or chunk < 0:
+            raise KernelError(f"attention: a chunk of {chunk} and a window of {window} at once")
+        window = chunk  # both bound the keys of a token; the kernels take a chunk as a negative window
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
     _need(k_cache, "key cache", qkv.dtype)
@@ -774,7 +781,8 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
                                            _c_int(num_kv_heads), _c_int(head_dim), _c_int(dv), _c_int(k_cache.shape[2]),
-                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), _ptr(terms.log_r1),
+                                           _c_int(-chunk if chunk else (window or 0)), _c_float(scale), _ptr(score_slopes),
+                                           _ptr(terms.log_r1),
                                            _ptr(terms.log_r2), _ptr(terms.sink), _c_int(v_stride), *extra, _stream()),
         "paged attention", 2 if extra and extra[0].value > 0 else 1,
     )
@@ -947,13 +955,15 @@ LINEAR_ATTENTION_SEGMENT = 128
 
 def linear_attention(qkv: torch.Tensor, offsets: tuple, out: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
                      ctx, heads: int, dim: int, vdim: int, silu: bool = False, write_state: bool = True,
-                     segment: Optional[int] = None):
+                     segment: Optional[int] = None, rotary: Optional["RotaryTable"] = None, k_scale: float = 1.0):
     """Decayed linear attention of the step's tokens, request by request from each request's state:
     S <- decay[h] S + k v^T, o = S^T q per head.  ``qkv`` rows hold q, k heads (heads x dim) and v heads
     (heads x vdim) at the column ``offsets`` (q, k, v); ``out`` fp32 [T, heads x vdim]; ``state`` fp32
     [slots, heads, vdim, dim].  ``silu``: q, k and v pass through SiLU on the way in.  A request that brings more
     than ``segment`` tokens (128 by default) runs as segments side by side: a pass that sums each segment alone, one
-    that carries the state from segment to segment, one that forms the outputs (scratch from the step's workspace)."""
+    that carries the state from segment to segment, one that forms the outputs (scratch from the step's workspace).
+    ``rotary``: q and k are rotated by the tokens' positions (``ctx.positions``) on their way in; ``k_scale``: k is then
+    multiplied by it.  Both in fp32, so what enters the recurrence is never rounded."""
     T, width, ld = _rows(qkv, "linear attention input")
     T2, n, ldo = _rows(out, "linear attention output")
     _need(state, "linear attention state", torch.float32)
@@ -977,7 +987,7 @@ def linear_attention(qkv: torch.Tensor, offsets: tuple, out: torch.Tensor, state
                                        _ptr(decay), _ptr(ctx.seq_q_start), _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs),
                                        _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(1 if silu else 0),
                                        _c_int(1 if write_state else 0), _c_int(seg), _c_int(segs_max), _ptr(scratch),
-                                       _stream()),
+                                       *_rotary_args(rotary, ctx, dim, qkv.device), _c_float(k_scale), _stream()),
         "linear attention", 1 if segs_max == 1 else 3,
     )
 
@@ -1263,6 +1273,141 @@ def head_gemm(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.T
     )
 
 
+class RotaryTable:
+    """A rotation of the first ``rotary_dim`` elements of a head by position x frequency: ``freq`` fp32 [rotary_dim / 2]
+    on the device; ``interleaved``: the pairs are the elements (2i, 2i + 1), else (i, i + rotary_dim / 2);
+    ``magnitude``: a factor on every cosine and sine."""
+
+    __slots__ = ("freq", "rotary_dim", "interleaved", "magnitude")
+
+    def __init__(self, freq: torch.Tensor, rotary_dim: int, interleaved: bool = False, magnitude: float = 1.0):
+        self.freq, self.rotary_dim = freq, int(rotary_dim)
+        self.interleaved, self.magnitude = bool(interleaved), float(magnitude)
+
+
+def _rotary_args(rotary: Optional[RotaryTable], ctx, head_dim: int, device) -> tuple:
+    """(positions, freq, rotary_dim, interleaved, magnitude) as the launchers take them; no rotation: null positions."""
+    if rotary is None or rotary.rotary_dim == 0:
+        return _ptr(None), _ptr(None), _c_int(0), _c_int(0), _c_float(1.0)
+    _need(rotary.freq, "rotary frequencies", torch.float32)
+    _need(ctx.positions, "positions", torch.int32)
+    if rotary.rotary_dim % 2 or rotary.rotary_dim > head_dim or rotary.freq.numel() != rotary.rotary_dim // 2:
+        raise KernelError(f"rotation of {rotary.rotary_dim} elements ({rotary.freq.numel()} frequencies) of heads of {head_dim}")
+    return (_ptr(ctx.positions), _ptr(rotary.freq), _c_int(rotary.rotary_dim), _c_int(1 if rotary.interleaved else 0),
+            _c_float(rotary.magnitude))
+
+
+def dynamic_tanh(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+                 row_index: Optional[torch.Tensor] = None):
+    """out[r] = tanh(alpha * x[row_index[r] or r]) * weight + bias, element by element in fp32 (``alpha``: one number on
+    the device); x fp32, out in the activations' type."""
+    _need(x, "dynamic tanh input", torch.float32)
+    _need(weight, "dynamic tanh weight", torch.float32)
+    _need(bias, "dynamic tanh bias", torch.float32)
+    _need(alpha, "dynamic tanh alpha", torch.float32)
+    _need(out, "dynamic tanh output")
+    rows, H = out.shape
+    if x.shape[1] != H or weight.numel() != H or bias.numel() != H or alpha.numel() != 1:
+        raise KernelError(f"dynamic tanh: x {tuple(x.shape)}, weight {tuple(weight.shape)}, bias {tuple(bias.shape)}, "
+                          f"alpha {tuple(alpha.shape)}")
+    if row_index is not None:
+        _need(row_index, "row index", torch.int32)
+        if row_index.numel() != rows:
+            raise KernelError("dynamic tanh: one row index per output row is needed")
+    elif x.shape[0] != rows:
+        raise KernelError("dynamic tanh: input and output row counts differ")
+    _check(_lib().ferris_dynamic_tanh(_ptr(x), _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(row_index), _ptr(out),
+                                      _c_int(_dt(out, "dynamic tanh output")), _c_int(rows), _c_int(H), _stream()),
+           "dynamic tanh")
+
+
+def softcap_(logits: torch.Tensor, cap: float):
+    """logits <- cap * tanh(logits / cap) in place; fp32."""
+    _need(logits, "logits", torch.float32)
+    _check(_lib().ferris_softcap(_ptr(logits), ctypes.c_longlong(logits.numel()), _c_float(cap), _stream()), "softcap")
+
+
+def qk_norm_rotary_cache_write(qkv: torch.Tensor, ctx, slot_mapping: Optional[torch.Tensor], k_cache, v_cache,
+                               num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
+                               q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                               rotary: Optional[RotaryTable], values_from_keys: bool = False, write_kv: bool = True):
+    """Between the q/k(/v) product and attention: q and k each divided by the root mean square of their WHOLE projection
+    (all heads at once) and multiplied by ``q_norm`` / ``k_norm`` (fp32, one number per element; None: no norm), then
+    rotated by the tokens' positions; q rewritten in place, k and the values into the paged cache.
+    ``values_from_keys``: the values are the keys as projected (before norm and rotation); the rows then hold
+    [nh d | nkv d] only."""
+    T, width, ld = _rows(qkv, "qkv")
+    want = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * v_head_dim)
+    if width != want:
+        raise KernelError(f"qk norm + rotation: rows of {width} for {num_heads}+{num_kv_heads} heads of {head_dim}")
+    for name, t_, n in (("q norm weight", q_norm, num_heads * head_dim), ("k norm weight", k_norm, num_kv_heads * head_dim)):
+        if t_ is not None:
+            _need(t_, name, torch.float32)
+            if t_.numel() != n:
+                raise KernelError(f"qk norm + rotation: {name} of {t_.numel()} for {n} elements")
+    page_size = 1
+    if write_kv:
+        _need(slot_mapping, "slot mapping", torch.int32)
+        _need(k_cache, "key cache", qkv.dtype)
+        _need(v_cache, "value cache", qkv.dtype)
+        page_size = k_cache.shape[2]
+        if (slot_mapping.numel() != T or k_cache.shape[1:] != (num_kv_heads, page_size, head_dim)
+                or v_cache.shape != (*k_cache.shape[:3], v_head_dim)):
+            raise KernelError(f"qk norm + rotation: caches {tuple(k_cache.shape)} {tuple(v_cache.shape)} do not fit")
+    positions, freq, rdim, inter, mag = _rotary_args(rotary, ctx, head_dim, qkv.device)
+    _need(ctx.positions, "positions", torch.int32)
+    _check(
+        _lib().ferris_qk_norm_rotary_cache_write(
+            _ptr(qkv), _c_int(ld), _c_int(_dt(qkv, "qkv")), _ptr(ctx.positions), _ptr(slot_mapping if write_kv else None),
+            _ptr(k_cache if write_kv else None), _ptr(v_cache if write_kv else None), _c_int(T), _c_int(num_heads),
+            _c_int(num_kv_heads), _c_int(head_dim), _c_int(v_head_dim), _c_int(page_size), _ptr(q_norm), _ptr(k_norm),
+            _c_float(eps), freq, rdim, inter, mag, _c_int(1 if values_from_keys else 0), _c_int(1 if write_kv else 0),
+            _stream()),
+        "qk norm + rotation + cache write",
+    )
+
+
+def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
+               weights: torch.Tensor, top: int):
+    """The ``top`` experts of every row of ``x`` and their weights: logits x weight^T + bias in fp32 sums, the largest
+    ``top`` (lowest index among equals), softmax over those alone.  ids int32 [T, top], weights fp32 [T, top]."""
+    T, W, ldx = _rows(x, "router input")
+    _need(weight, "router matrix", x.dtype)
+    _need(ids, "expert ids", torch.int32)
+    _need(weights, "expert weights", torch.float32)
+    E = weight.shape[0]
+    if weight.shape != (E, W) or ids.shape != (T, top) or weights.shape != (T, top) or (bias is not None and bias.numel() != E):
+        raise KernelError(f"router: x {tuple(x.shape)}, matrix {tuple(weight.shape)}, ids {tuple(ids.shape)}")
+    if bias is not None:
+        _need(bias, "router bias", torch.float32)
+    _check(_lib().ferris_moe_router(_ptr(x), _c_int(ldx), _c_int(_dt(x, "router")), _ptr(weight), _ptr(bias), _ptr(ids),
+                                    _ptr(weights), _c_int(T), _c_int(W), _c_int(E), _c_int(top), _stream()), "router")
+
+
+def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+                weights: torch.Tensor, h: torch.Tensor, workspace=None, accumulate: bool = True):
+    """h (+)= sum over a row's chosen experts of weight x down_e (silu(gate_e x) * (up_e x)).  gate, up [E, ff, W],
+    down [E, W, ff] in x's type; ids int32 and weights fp32 [T, top]; h fp32 [T, W]."""
+    T, W, ldx = _rows(x, "experts input")
+    T2, W2, ldh = _rows(h, "experts output")
+    _need(gate, "gate matrices", x.dtype)
+    _need(up, "up matrices", x.dtype)
+    _need(down, "down matrices", x.dtype)
+    _need(ids, "expert ids", torch.int32)
+    _need(weights, "expert weights", torch.float32)
+    E, ff = gate.shape[0], gate.shape[1]
+    top = ids.shape[1]
+    if (gate.shape != (E, ff, W) or up.shape != (E, ff, W) or down.shape != (E, W, ff) or (T2, W2) != (T, W)
+            or h.dtype != torch.float32 or ids.shape != (T, top) or weights.shape != (T, top)):
+        raise KernelError(f"experts: x {tuple(x.shape)}, gate {tuple(gate.shape)}, down {tuple(down.shape)}, ids {tuple(ids.shape)}")
+    act = workspace.get("moe_act", (T * top, ff), x.dtype) if workspace is not None else \
+        torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
+    _check(_lib().ferris_moe_experts_token_major(_ptr(x), _c_int(ldx), _c_int(_dt(x, "experts")), _ptr(gate), _ptr(up),
+                                                 _ptr(down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(h), _c_int(ldh),
+                                                 _c_int(T), _c_int(W), _c_int(ff), _c_int(top),
+                                                 _c_int(1 if accumulate else 0), _stream()), "experts", 2)
+
+
 def kernel_status() -> int:
     """Reads and clears the device status word (synchronises).  0: no kernel gave up a bounded wait;
     otherwise (code << 16) | place."""
@@ -1413,8 +1558,11 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
-                    score_slopes=None, v_head_dim: Optional[int] = None, values_in_keys: bool = False):
+                    score_slopes=None, v_head_dim: Optional[int] = None, values_in_keys: bool = False,
+                    chunk: int = 0, fp32_weights: bool = False):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
+    ``chunk``: see ``paged_attention_simt``.  ``fp32_weights``: the softmax's weights and the weighted sum stay in 32-bit
+    (the tensor-core kernels round the weights to bf16 for their second product), so the general kernel runs.
     ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV
     kernel when every request brings one token, the prefill kernel otherwise; every other geometry, the
     32-bit path, scores with slopes added (``score_slopes``) and value heads of another size than the keys'
@@ -1422,11 +1570,11 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
     _need(k_cache, "key cache", qkv.dtype)
     if isinstance(score_slopes, ScoreTerms) and not score_slopes.any():
         score_slopes = None
-    if values_in_keys or (v_head_dim is not None and v_head_dim != head_dim):
+    if values_in_keys or chunk or fp32_weights or (v_head_dim is not None and v_head_dim != head_dim):
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
                              num_kv_heads, head_dim, window, scale, score_slopes=score_slopes, v_head_dim=v_head_dim,
                              max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, workspace=ctx.workspace,
-                             values_in_keys=values_in_keys)
+                             values_in_keys=values_in_keys, chunk=chunk)
         return
     _need(v_cache, "value cache", qkv.dtype)
     _need(block_tables, "block tables", torch.int32)

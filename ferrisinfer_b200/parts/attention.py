@@ -22,6 +22,16 @@ Options beyond the reference's layer, each a parameter of its own:
                         ``bias_names`` names those of q, k and v)
   ``sink_name``         a learned number per head under that name: the softmax's denominator also holds its
                         exponential, a weight that belongs to no key and no value (unscaled, unbiased, counted once)
+  ``values_from_keys``  there is no value matrix: a token's values are its keys as projected (before any norm or rotation)
+  ``qk_norm``           {"eps", "q", "k"}: q and k each divided by sqrt(mean(.^2) + eps) over their WHOLE projection (all
+                        heads at once) and multiplied by the weights named ``q`` and ``k`` under the prefix (one number
+                        per element of the projection), before the rotation
+  ``chunk``             instead of a window: positions are counted off in chunks of that many from 0, and a token
+                        sees the keys of its own chunk up to itself
+  ``fp32_weights``      the softmax's weights and the weighted sum of values stay in 32-bit (the general kernel)
+  a ``scaled_rotary`` position encoding (either pair layout, part of a head, scaled frequencies) rotates in the kernel
+  that also norms and writes the cache; it goes with ``qk_norm``, ``values_from_keys``, ``chunk`` and value heads of
+  their own size, not with the unit norm or the temperature
 With any of these but the names the step runs product -> norm / temperature / cache write -> attention -> product;
 the position encoding must then be one that rotates nothing (it may add slopes or a logarithmic distance penalty to
 the scores; one with learned numbers names them under the mixer's prefix).
@@ -52,7 +62,9 @@ class GroupedQueryAttention(Mixer):
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None,
                  v_head_dim: Optional[int] = None, qk_unit_norm_eps: Optional[float] = None,
                  query_temperature: Optional[tuple] = None, tensor_names: Optional[dict] = None,
-                 bias_names: Optional[dict] = None, sink_name: Optional[str] = None):
+                 bias_names: Optional[dict] = None, sink_name: Optional[str] = None,
+                 values_from_keys: bool = False, qk_norm: Optional[dict] = None, chunk: Optional[int] = None,
+                 fp32_weights: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
@@ -68,16 +80,32 @@ class GroupedQueryAttention(Mixer):
             if int(every) <= 0:
                 raise ValueError(f"the query temperature grows every {every} positions: a positive count is needed")
             self.query_temperature = (float(coef), int(every))
+        self.values_from_keys, self.fp32_weights = bool(values_from_keys), bool(fp32_weights)
+        self.chunk = None if chunk is None else int(chunk)
+        if self.chunk is not None and (self.chunk <= 0 or self.window is not None):
+            raise ValueError(f"a chunk of {chunk} keys (a positive count, and no window beside it)")
+        if self.values_from_keys and self.v_head_dim != self.head_dim:
+            raise ValueError(f"keys of {self.head_dim} cannot serve as values of {self.v_head_dim}")
+        self.qk_norm = None
+        if qk_norm is not None:
+            self.qk_norm = (float(qk_norm["eps"]), qk_norm.get("q", "q.norm"), qk_norm.get("k", "k.norm"))
+        self.q_norm_weight = self.k_norm_weight = None
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
-        self.v_size = self.num_kv_heads * self.v_head_dim
+        self.v_size = 0 if self.values_from_keys else self.num_kv_heads * self.v_head_dim
         self.o_size = self.num_heads * self.v_head_dim
         # the plain layer (the reference's) keeps its fused kernels; any option sends the step the general way
         self.sink_name, self.sink = sink_name, None
+        # norm over the whole projection, rotation of either layout and the cache write are one kernel of their own
+        self.rotary_prepare = hasattr(self.position, "table") or self.qk_norm is not None or self.values_from_keys
+        if self.rotary_prepare and (self.qk_unit_norm_eps is not None or self.query_temperature is not None):
+            raise ValueError("a norm over the whole projection, a scaled rotation or values taken from the keys do not "
+                             "go with unit-normed heads or a query temperature")
         self.plain = (self.v_head_dim == self.head_dim and self.qk_unit_norm_eps is None
-                      and self.query_temperature is None and sink_name is None
+                      and self.query_temperature is None and sink_name is None and not self.rotary_prepare
+                      and self.chunk is None and not self.fp32_weights
                       and not getattr(self.position, "learned_scores", False))
-        if not self.plain and getattr(self.position, "rotary_dim", 0):
+        if not self.plain and not hasattr(self.position, "table") and getattr(self.position, "rotary_dim", 0):
             raise ValueError("unit-norm keys, a query temperature or value heads of their own size go with a "
                              "position encoding that rotates nothing")
         self.tensor_names = dict(tensor_names) if tensor_names else None
@@ -95,34 +123,46 @@ class GroupedQueryAttention(Mixer):
         specs = [
             TensorSpec(self._matrix_name(prefix, "q"), (Q, H), "matrix"),
             TensorSpec(self._matrix_name(prefix, "k"), (KV, H), "matrix"),
-            TensorSpec(self._matrix_name(prefix, "v"), (self.v_size, H), "matrix"),
         ]
+        if not self.values_from_keys:
+            specs.append(TensorSpec(self._matrix_name(prefix, "v"), (self.v_size, H), "matrix"))
+        if self.qk_norm is not None:
+            specs += [TensorSpec(f"{prefix}.{self.qk_norm[1]}", (Q,), "norm"),
+                      TensorSpec(f"{prefix}.{self.qk_norm[2]}", (KV,), "norm")]
         if self.bias_names:
             specs += [TensorSpec(f"{prefix}.{self.bias_names[n]}", (size,), "bias")
-                      for n, size in zip("qkv", (Q, KV, self.v_size))]
+                      for n, size in zip(self._inputs, (Q, KV, self.v_size))]
         elif not self.tensor_names:
             specs += [
                 TensorSpec(f"{prefix}.q_proj.bias", (Q,), "bias", required=False),
                 TensorSpec(f"{prefix}.k_proj.bias", (KV,), "bias", required=False),
                 TensorSpec(f"{prefix}.v_proj.bias", (self.v_size,), "bias", required=False),
-            ]
+            ][:len(self._inputs)]
         specs += self.position.tensor_specs(prefix)  # learned numbers of the position encoding, if it has any
         if self.sink_name:
             specs.append(TensorSpec(f"{prefix}.{self.sink_name}", (self.num_heads,), "vector"))
         return specs + [TensorSpec(self._matrix_name(prefix, "o"), (H, self.o_size), "matrix")]
 
+    @property
+    def _inputs(self) -> str:
+        """The projections the folder holds, one letter each."""
+        return "qk" if self.values_from_keys else "qkv"
+
     def bind(self, tensors, prefix):
-        w = [tensors.pop(self._matrix_name(prefix, n)) for n in "qkv"]
+        w = [tensors.pop(self._matrix_name(prefix, n)) for n in self._inputs]
         self.qkv_weight = torch.cat(w, dim=0).contiguous()
         if self.bias_names:
-            biases = [tensors.pop(f"{prefix}.{self.bias_names[n]}") for n in "qkv"]
+            biases = [tensors.pop(f"{prefix}.{self.bias_names[n]}") for n in self._inputs]
         else:
-            biases = [None if self.tensor_names else tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in "qkv"]
+            biases = [None if self.tensor_names else tensors.pop(f"{prefix}.{n}_proj.bias", None) for n in self._inputs]
+        if self.qk_norm is not None:
+            self.q_norm_weight = tensors[f"{prefix}.{self.qk_norm[1]}"]
+            self.k_norm_weight = tensors[f"{prefix}.{self.qk_norm[2]}"]
         self.position.bind(tensors, prefix)
         if self.sink_name:
             self.sink = tensors[f"{prefix}.{self.sink_name}"]
         if any(b is not None for b in biases):
-            sizes = (self.q_size, self.kv_size, self.v_size)
+            sizes = (self.q_size, self.kv_size, self.v_size)[:len(biases)]
             parts = [
                 b if b is not None else torch.zeros(n, dtype=torch.float32, device=self.qkv_weight.device)
                 for b, n in zip(biases, sizes)
@@ -135,7 +175,7 @@ class GroupedQueryAttention(Mixer):
     # -------------------------------------------------------------------- cache
     def cache_need(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window,
-                       None if self.v_head_dim == self.head_dim else self.v_head_dim)
+                       None if self.v_head_dim == self.head_dim else self.v_head_dim, chunk=self.chunk)
 
     # ------------------------------------------------------------------ forward
     def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
@@ -146,14 +186,22 @@ class GroupedQueryAttention(Mixer):
         if not self.plain:
             dv = self.v_head_dim
             ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
-            ops.qk_prepare_cache_write(qkv, ctx.positions, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
-                                       self.qk_unit_norm_eps, self.query_temperature, write_kv=owns_cache)
+            if self.rotary_prepare:
+                rotary = self.position.table(qkv.device) if hasattr(self.position, "table") else None
+                ops.qk_norm_rotary_cache_write(qkv, ctx, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
+                                               self.q_norm_weight, self.k_norm_weight,
+                                               self.qk_norm[0] if self.qk_norm else 0.0, rotary,
+                                               values_from_keys=self.values_from_keys, write_kv=owns_cache)
+            else:
+                ops.qk_prepare_cache_write(qkv, ctx.positions, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
+                                           self.qk_unit_norm_eps, self.query_temperature, write_kv=owns_cache)
             out = ctx.workspace.get("attn_out", (T, self.o_size), x.dtype)
             log = self.position.score_log_penalty(nh, qkv.device)
             terms = ops.ScoreTerms(slopes=self.position.score_slopes(nh, qkv.device), sink=self.sink,
                                    log_r1=None if log is None else log[0], log_r2=None if log is None else log[1])
             ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d, self.window or 0,
-                                self.scale, score_slopes=terms, v_head_dim=dv)
+                                self.scale, score_slopes=terms, v_head_dim=dv, chunk=self.chunk or 0,
+                                fp32_weights=self.fp32_weights)
             ops.gemm(out, self.o_weight, None, h, accumulate=accumulate)
             return
         table = self.position.rotary_table(qkv.device)

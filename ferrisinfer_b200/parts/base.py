@@ -26,6 +26,8 @@ class PagedKV:
     """The mixer keeps a key and a value of ``num_kv_heads x head_dim`` per token, in pages.
     ``window``: None = every past token is read; n = only the last n (the current one included),
     so pages that lie wholly behind the window are given back while the request runs.
+    ``chunk``: positions are counted off in chunks of that many from 0 and a token reads the keys of its own chunk only, so
+    the pages of chunks that are over are given back while the request runs (not together with ``window``).
     ``v_head_dim``: size of a value head where it differs from a key head's (None = the same; 0 = no value rows are
     kept, for a mixer whose keys carry their values)."""
 
@@ -33,6 +35,20 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    def first_needed(self, num_tokens: int) -> int:
+        """The lowest position that a query at position ``num_tokens`` or later can still read."""
+        if self.chunk is not None:
+            return num_tokens - num_tokens % self.chunk
+        if self.window is not None:
+            return max(0, num_tokens - self.window + 1)
+        return 0
+
+    @property
+    def keeps_all(self) -> bool:
+        """Whether every key stays readable as long as the request lives."""
+        return self.window is None and self.chunk is None
 
     @property
     def value_dim(self) -> int:

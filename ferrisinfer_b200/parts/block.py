@@ -1,7 +1,7 @@
 """How a layer's parts are arranged.
 
 The pre-norm residual block, one branch after the other:
-  h += mixer(norm_1(h));  h += feed_forward(norm_2(h))
+  h += mixer(norm_1(h));  h += feed_forward(norm_2(h))          (a layer may have no feed-forward: the first half alone)
 (crates/ferrisinfer-runtime/src/reference.rs:244-249, 331-344, 362-368).
 
 The parallel block, both branches from the same h:
@@ -29,21 +29,26 @@ class PreNormResidualBlock(Block):
 
     def _children(self, prefix):
         m, f, n1, n2 = self._names
-        return [
+        return [(part, p) for part, p in (
             (self.mixer_norm, f"{prefix}.{n1}"),
             (self.mixer, f"{prefix}.{m}"),
             (self.feed_forward_norm, f"{prefix}.{n2}"),
             (self.feed_forward, f"{prefix}.{f}"),
-        ]
+        ) if part is not None]
 
     def tensor_specs(self, prefix):
         out = []
         for part, p in self._children(prefix):
-            out += part.tensor_specs(p)
+            specs = part.tensor_specs(p)
+            if part is self.feed_forward_norm and self.feed_forward is None:  # read if the folder has it, and not used
+                specs = [TensorSpec(s.name, s.shape, s.role, required=False) for s in specs]
+            out += specs
         return out
 
     def bind(self, tensors, prefix):
         for part, p in self._children(prefix):
+            if part is self.feed_forward_norm and self.feed_forward is None:
+                continue
             part.bind(tensors, p)
 
     def cache_need(self):
@@ -51,7 +56,8 @@ class PreNormResidualBlock(Block):
 
     @property
     def graph_safe(self):
-        return bool(getattr(self.mixer, "graph_safe", False) and getattr(self.feed_forward, "graph_safe", False))
+        return bool(getattr(self.mixer, "graph_safe", False)
+                    and (self.feed_forward is None or getattr(self.feed_forward, "graph_safe", False)))
 
     def forward(self, h, ctx, cache, owns_cache):
         buf = ctx.workspace.get("block_normed", (h.shape[0], self.hidden_size), ctx.act_dtype)
@@ -59,6 +65,8 @@ class PreNormResidualBlock(Block):
         if not getattr(self.mixer, "accepts_lazy_norm", False) and hasattr(x, "materialize"):
             x = x.materialize()
         self.mixer.forward(x, h, ctx, cache, owns_cache)
+        if self.feed_forward is None:  # a layer of the mixer's branch alone
+            return
         x = self.feed_forward_norm.lazy(h, buf)
         if not getattr(self.feed_forward, "accepts_lazy_norm", False) and hasattr(x, "materialize"):
             x = x.materialize()

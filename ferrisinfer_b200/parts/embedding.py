@@ -16,15 +16,19 @@ from .plan import register_part
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight_name = weight_name  # "" = the tensor is named by the prefix itself
         self.weight = None
 
+    def _name(self, prefix):
+        return f"{prefix}.{self.weight_name}" if self.weight_name else prefix
+
     def tensor_specs(self, prefix):
-        return [TensorSpec(f"{prefix}.weight", (self.vocab_size, self.hidden_size), "embedding")]
+        return [TensorSpec(self._name(prefix), (self.vocab_size, self.hidden_size), "embedding")]
 
     def bind(self, tensors, prefix):
-        self.weight = tensors[f"{prefix}.weight"]
+        self.weight = tensors[self._name(prefix)]
 
     def forward(self, token_ids, h):
         ops.embed_gather(self.weight, token_ids, h)
@@ -70,10 +74,15 @@ class ScaledSinusoidalEmbedding(Part):
 
 class OutputHead(Part):
     """``tied_to``: tensor name of the embedding table to use as the output matrix, or None
-    when the folder has a matrix of its own under ``prefix``."""
+    when the folder has a matrix of its own under ``prefix``.  ``softcap``: the logits z become
+    softcap * tanh(z / softcap) (None: they stay as they are)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to=None, weight_name: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to=None, weight_name: str = "weight",
+                 softcap: float = None):
         self.vocab_size, self.hidden_size, self.tied_to = int(vocab_size), int(hidden_size), tied_to
+        self.softcap = None if not softcap else float(softcap)
+        if self.softcap is not None and not (self.softcap > 0.0):
+            raise ValueError(f"a soft cap of {softcap}: a positive number is needed")
         self.weight_name = weight_name  # "" = the tensor is named by the prefix itself
         self.weight = None
 
@@ -91,11 +100,19 @@ class OutputHead(Part):
     def forward(self, y, logits):
         """logits fp32 [n, V] = y [n, H] W^T."""
         ops.gemm(y, self.weight, None, logits)
+        if self.softcap is not None:
+            ops.softcap_(logits, self.softcap)
 
     def forward_greedy(self, y, tokens, probs, workspace):
         """tokens int32 [n] = the index of each row's greatest logit (the lowest among equals), probs fp32 [n] its
         softmax probability; the logits themselves are stored nowhere where a kernel can avoid it (the reference's
         fused product + argmax: crates/ferrisinfer-kernel/src/cpu/matmul.rs:190-274)."""
+        if self.softcap is not None:
+            # the cap keeps the order of the logits but changes the probabilities: logits, cap, then the greedy rows
+            logits = workspace.get("logits", (y.shape[0], self.vocab_size), torch.float32)
+            self.forward(y, logits)
+            ops.sample(logits, tokens, probs)
+            return
         ops.greedy_head(y, self.weight, tokens, probs, workspace)
 
 

@@ -1,4 +1,5 @@
-"""Feed-forwards as parts: the gated SiLU one (SwiGLU), and a plain one with a choice of activation.
+"""Feed-forwards as parts: the gated SiLU one (SwiGLU), a plain one with a choice of activation, and a mixture of
+gated SiLU experts of which every token uses a few.
 
   u = y W_up^T;  g = y W_gate^T;  m = u * (g * sigmoid(g));  h += m W_down^T
 (crates/ferrisinfer-runtime/src/reference.rs:346-368; the reference's w1 is up_proj and w3 is
@@ -90,5 +91,57 @@ class DenseActivation(FeedForward):
         ops.gemm(z, self.down, None, h, accumulate=accumulate)
 
 
+class MixtureOfExperts(FeedForward):
+    """h += sum over the token's ``top`` experts of weight_e W_down_e (silu(W_gate_e y) * (W_up_e y)).
+
+    Router: z = W_r y + b_r in fp32 sums; the ``top`` largest z (the lowest index among equals); the weights are the
+    softmax over those alone.  Experts have no biases.  Tensors under the prefix: ``router`` [experts, H],
+    ``router.b`` [experts], and for expert i ``e<i>.gate`` / ``e<i>.up`` [ff, H], ``e<i>.down`` [H, ff]; on the device
+    the experts' matrices are stacked ([experts, ff, H] and [experts, H, ff]) so that kernels address an expert by
+    its index."""
+
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, router_name: str = "router",
+                 router_bias_name: str = "router.b", expert_prefix: str = "e", gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.experts, self.top = int(experts), int(top)
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"{self.top} of {self.experts} experts cannot be chosen")
+        self._names = (router_name, router_bias_name, expert_prefix, gate_name, up_name, down_name)
+        self.router = self.router_bias = self.gate = self.up = self.down = None
+
+    def _expert(self, prefix, e, which):
+        return f"{prefix}.{self._names[2]}{e}.{which}"
+
+    def tensor_specs(self, prefix):
+        H, I = self.hidden_size, self.intermediate_size
+        r, rb, _, g, u, d = self._names
+        specs = []
+        for e in range(self.experts):
+            specs += [TensorSpec(self._expert(prefix, e, g), (I, H), "matrix"),
+                      TensorSpec(self._expert(prefix, e, u), (I, H), "matrix"),
+                      TensorSpec(self._expert(prefix, e, d), (H, I), "matrix")]
+        return specs + [TensorSpec(f"{prefix}.{r}", (self.experts, H), "matrix"),
+                        TensorSpec(f"{prefix}.{rb}", (self.experts,), "bias")]
+
+    def bind(self, tensors, prefix):
+        r, rb, _, g, u, d = self._names
+        self.gate = torch.stack([tensors.pop(self._expert(prefix, e, g)) for e in range(self.experts)]).contiguous()
+        self.up = torch.stack([tensors.pop(self._expert(prefix, e, u)) for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([tensors.pop(self._expert(prefix, e, d)) for e in range(self.experts)]).contiguous()
+        self.router, self.router_bias = tensors[f"{prefix}.{r}"], tensors[f"{prefix}.{rb}"]
+
+    def forward(self, x, h, ctx, accumulate: bool = True):
+        T = x.shape[0]
+        ids = ctx.workspace.get("moe_ids", (T, self.top), torch.int32)
+        weights = ctx.workspace.get("moe_weights", (T, self.top), torch.float32)
+        ops.moe_router(x, self.router, self.router_bias, ids, weights, self.top)
+        ops.moe_experts(x, self.gate, self.up, self.down, ids, weights, h, ctx.workspace, accumulate=accumulate)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "mixture_of_experts", MixtureOfExperts)
 register_part("feed_forward", "dense_activation", DenseActivation)

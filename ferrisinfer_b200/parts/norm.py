@@ -3,6 +3,9 @@
   ms = sum(x^2) / H;  r = 1 / sqrt(ms + eps);  y_j = (x_j * r) * w_j
 (crates/ferrisinfer-kernel/src/cpu/reduction.rs:35-41).
 
+``DynamicTanh``: no statistics at all: y_j = tanh(alpha x_j) * w_j + b_j with one learned number alpha; the tensors are
+``weight_name``, ``<weight_name>.<alpha_name>`` and ``<weight_name>.<bias_name>`` under the part's prefix.
+
 ``GroupedRMSNorm``: the row in ``groups`` equal consecutive parts, each divided by its own root mean square; the
 weight spans the whole row.  The tensor is named by ``weight_name`` under the part's prefix ("" = the prefix itself).
 """
@@ -69,5 +72,33 @@ class GroupedRMSNorm(Norm):
         return True
 
 
+class DynamicTanh(Norm):
+    """tanh(alpha * x) * weight + bias, element by element in fp32; ``eps`` is accepted and unused (the norm divides by
+    nothing)."""
+
+    def __init__(self, hidden_size: int, eps: float = 0.0, weight_name: str = "weight", alpha_name: str = "alpha",
+                 bias_name: str = "b"):
+        self.hidden_size = int(hidden_size)
+        self.weight_name, self.alpha_name, self.bias_name = weight_name, alpha_name, bias_name
+        self.weight = self.bias = self.alpha = None
+
+    def _names(self, prefix):
+        w = f"{prefix}.{self.weight_name}" if self.weight_name else prefix
+        return w, f"{w}.{self.alpha_name}", f"{w}.{self.bias_name}"
+
+    def tensor_specs(self, prefix):
+        w, a, b = self._names(prefix)
+        return [TensorSpec(w, (self.hidden_size,), "norm"), TensorSpec(b, (self.hidden_size,), "bias"),
+                TensorSpec(a, (), "norm")]
+
+    def bind(self, tensors, prefix):
+        w, a, b = self._names(prefix)
+        self.weight, self.bias, self.alpha = tensors[w], tensors[b], tensors[a].reshape(1)
+
+    def forward(self, h, out, row_index=None):
+        ops.dynamic_tanh(h, self.weight, self.bias, self.alpha, out, row_index)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)
 register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

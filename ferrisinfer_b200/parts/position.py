@@ -8,6 +8,13 @@ in f32 (crates/ferrisinfer-kernel/src/cpu/attention.rs:1254-1276):
 rotary_dim).  The angle ``float(pos) * inv_freq[i]`` and its sine and cosine
 are fp32, formed in the kernel that also writes the cache.
 
+``ScaledRotary``: a rotation of the first ``rotary_dim`` elements of a head with frequencies
+``base ** (-2 i / rotary_dim)`` (formed in 64-bit on the host, rounded once), pairs laid out (i, i + rotary_dim / 2)
+("half") or (2i, 2i + 1) ("interleaved"), optionally with YaRN scaling: with c(r) = rotary_dim ln(original / (2 pi r)) /
+(2 ln base), lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) /
+max(hi - lo, 0.001), 0, 1), frequency i becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and every cosine and sine is
+multiplied by 0.1 ln(factor) + 1.  It is applied by the kernel that prepares a mixer's queries and keys.
+
 ``NoPosition``: nothing is encoded (the keys go to the cache as they are).
 
 ``DistanceSlopes``: nothing is rotated; the score of the key at position j for the query at position P loses
@@ -15,6 +22,8 @@ slope_h * (P - j), with slope_h = 2^(-span (h + 1) / heads) for head h = 0 .. he
 """
 
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -65,6 +74,51 @@ class RotaryEncoding(PositionEncoding):
             ops.rotary_angles(ctx.positions, inv_freq, angles)
             ctx.shared[key] = angles
         return angles
+
+
+class ScaledRotary(PositionEncoding):
+    graph_safe = True
+
+    def __init__(self, rotary_dim: int, base: float, layout: str = "half", scaling: dict = None):
+        """``scaling``: None, or the four numbers ``factor``, ``original``, ``fast``, ``slow`` of a YaRN scaling."""
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary layout '{layout}' is not known (half, interleaved)")
+        if rotary_dim < 0 or rotary_dim % 2:
+            raise ValueError(f"{rotary_dim} rotated elements: an even count is needed")
+        self.rotary_dim, self.base, self.layout = int(rotary_dim), float(base), layout
+        self.scaling = dict(scaling) if scaling else None
+        R = self.rotary_dim
+        freq = [self.base ** (-2.0 * i / R) for i in range(R // 2)]
+        self.magnitude = 1.0
+        if self.scaling and R:
+            factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+            fast, slow = float(self.scaling["fast"]), float(self.scaling["slow"])
+            if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0 or self.base <= 1.0:
+                raise ValueError(f"rotary scaling {self.scaling} with base {self.base}: positive numbers and a base above one")
+
+            def crossing(r):
+                return R * math.log(original / (2.0 * math.pi * r)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(crossing(fast)), 0)
+            hi = min(math.ceil(crossing(slow)), R - 1)
+            for i, f in enumerate(freq):
+                ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                freq[i] = f / factor * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
+        self._host = np.asarray(freq, dtype=np.float64).astype(np.float32)
+        self._device = {}
+
+    def rotary_table(self, device=None):
+        return None  # not the plain layer's rotation: the mixer asks for ``table`` instead
+
+    def table(self, device=None) -> "ops.RotaryTable":
+        """What the kernels take: frequencies on ``device``, layout, the factor on cosines and sines."""
+        device = torch.device(device if device is not None else "cuda")
+        key = str(device)
+        if key not in self._device:
+            self._device[key] = ops.RotaryTable(torch.from_numpy(self._host.copy()).to(device), self.rotary_dim,
+                                                self.layout == "interleaved", self.magnitude)
+        return self._device[key]
 
 
 class NoPosition(PositionEncoding):
@@ -123,6 +177,7 @@ class LogDistancePenalty(PositionEncoding):
 
 
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "scaled_rotary", ScaledRotary)
 register_part("position", "log_distance_penalty", LogDistancePenalty)
 register_part("position", "distance_slopes", DistanceSlopes)
 register_part("position", "none", NoPosition)
