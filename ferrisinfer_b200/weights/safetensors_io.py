@@ -180,7 +180,7 @@ def write_safetensors(path: str, tensors: dict[str, torch.Tensor]) -> None:
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise WeightFileError(f"cannot store tensor '{name}' of dtype {t.dtype}")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # reshape first: a tensor without dimensions has no bytes view
         header[name] = {
             "dtype": _NAMES[t.dtype],
             "shape": list(t.shape),

@@ -125,9 +125,16 @@ def chunk_attention(y, w, prefix, mixer, eps, start=0, past=None):
     return o.reshape(T, H * d) @ w[prefix + ".o"].T, (kn, v)
 
 
-def mixture(y, w, prefix, mlp):
+def mixture(y, w, prefix, mlp, margins=None):
+    """``margins`` (a list with one entry per token, or None): lowered to the gap between the last chosen logit and the
+    first that is not, over the logits' spread, where that is smaller: how close the choice was."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = y @ w[prefix + ".router"].T + w[prefix + ".router.b"]
+    if margins is not None and top < E:
+        ordered = torch.sort(z, dim=-1, descending=True).values
+        gap = (ordered[:, top - 1] - ordered[:, top]) / (ordered[:, 0] - ordered[:, -1])
+        for t in range(y.shape[0]):
+            margins[t] = min(margins[t], float(gap[t]))
     out = torch.zeros(y.shape[0], w[prefix + ".e0.down"].shape[0], dtype=y.dtype)
     for t in range(y.shape[0]):
         chosen = sorted(range(E), key=lambda e: -float(z[t, e]))[:top]
@@ -144,9 +151,10 @@ def norm_of(x, w, name):
     return dynamic_tanh(x, w[name], w[name + ".b"], w[name + ".alpha"])
 
 
-def forward(cfg, w, ids, start=0, state=None, dtype=torch.float64, after_layer=None):
+def forward(cfg, w, ids, start=0, state=None, dtype=torch.float64, after_layer=None, margins=None):
     """Logits [len(ids), vocab] of the tokens ``ids`` at positions start .. and the state to continue from.
-    ``state``: what an earlier call returned (one entry per layer), or None at position 0."""
+    ``state``: what an earlier call returned (one entry per layer), or None at position 0.  ``after_layer(i, x)`` sees
+    the residual stream after every layer; ``margins``: see ``mixture`` (one entry per token, initially large)."""
     w = {k: v.to(dtype) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(list(ids), dtype=torch.long)]
@@ -164,7 +172,7 @@ def forward(cfg, w, ids, start=0, state=None, dtype=torch.float64, after_layer=N
         new_state.append(s)
         x = x + m
         if layer.get("mlp") is not None:
-            x = x + mixture(norm_of(x, w, p + ".norm2"), w, p + ".mlp", layer["mlp"])
+            x = x + mixture(norm_of(x, w, p + ".norm2"), w, p + ".mlp", layer["mlp"], margins)
         if after_layer is not None:
             after_layer(i, x)
     logits = norm_of(x, w, "final.norm") @ w["embed"].T
