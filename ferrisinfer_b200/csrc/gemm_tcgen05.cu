@@ -683,7 +683,20 @@ struct PTParams {
     int* status;
     RopeEpilogue rope;  // mode QKV_ROPE_BF16 only
     FerrisEpilogueAct act;  // applied by the bf16 store (mode STORE_BF16)
+    // A product per group of token tiles (a mixture of experts whose rows lie sorted by expert, every expert's rows
+    // filled up to whole tiles): tile_expert[m tile] = the expert whose weights the tile's rows meet, or -1 for a tile
+    // without rows, which is skipped; the experts' matrices lie stacked, expert_rows rows each.  Null: one matrix.
+    // Written by the launch before this one, so never read through a read-only path.
+    const int* tile_expert = nullptr;
+    int expert_rows = 0;
 };
+
+// The first weight row of the expert that token tile `mt` meets (0 without experts), or -1 to skip the tile.
+__device__ __forceinline__ int pt_tile_weight_row(const PTParams& p, int mt) {
+    if (!p.tile_expert) return 0;
+    const int e = *(reinterpret_cast<const volatile int*>(p.tile_expert) + mt);
+    return e < 0 ? -1 : e * p.expert_rows;
+}
 
 // The epilogue of one q/k/v tile for one warp: its 32 tokens (lane = token t) and every second item of 64
 // accumulator columns.  An item is a low and a high chunk of 32 columns of ONE head, d/2 apart, so that a thread
@@ -870,6 +883,8 @@ __global__ void __launch_bounds__(PT_THREADS)
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int wrow = pt_tile_weight_row(p, tile % p.m_tiles);
+                if (wrow < 0) continue;
                 const int m0 = (tile % p.m_tiles) * PT_BLOCK_M, n0 = (tile / p.m_tiles) * p.bn;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int s = it % PT_STAGES;
@@ -880,8 +895,9 @@ __global__ void __launch_bounds__(PT_THREADS)
                     uint8_t* st = smem + (size_t)s * stage_bytes;
                     mbar_expect_tx(&full[s], stage_bytes);
                     tma_load_2d(st, &map_x, kb * BLOCK_K, m0, &full[s]);
-                    tma_load_2d(st + a_bytes, &map_w, kb * BLOCK_K, n0, &full[s]);
-                    if (ACCS == 2) tma_load_2d(st + a_bytes + b_bytes, &map_w, kb * BLOCK_K, p.up_row_offset + n0, &full[s]);
+                    tma_load_2d(st + a_bytes, &map_w, kb * BLOCK_K, wrow + n0, &full[s]);
+                    if (ACCS == 2)
+                        tma_load_2d(st + a_bytes + b_bytes, &map_w, kb * BLOCK_K, wrow + p.up_row_offset + n0, &full[s]);
                 }
             }
         }
@@ -890,10 +906,12 @@ __global__ void __launch_bounds__(PT_THREADS)
             const uint32_t idesc = umma_idesc_bf16(PT_BLOCK_M, p.bn);
             int it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                if (pt_tile_weight_row(p, tile % p.m_tiles) < 0) continue;  // skipped by every role alike
                 const int buf = local & 1;
                 // the epilogue must have drained this accumulator buffer (two tiles ago)
                 if (local >= 2 && !mbar_wait(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status, 21)) break;
+                ++local;
                 tcgen05_fence_after();
                 const uint32_t d0 = tmem + buf * acc_cols;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
@@ -925,11 +943,13 @@ __global__ void __launch_bounds__(PT_THREADS)
         const int quarter = warp & 3, half = e >> 2;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         int local = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            if (pt_tile_weight_row(p, tile % p.m_tiles) < 0) continue;
             const int buf = local & 1;
             const int m0 = (tile % p.m_tiles) * PT_BLOCK_M, n0 = (tile / p.m_tiles) * p.bn;
             const int t = m0 + quarter * 32 + lane;
             if (!mbar_wait(&tmem_full[buf], (local >> 1) & 1, p.status, 23)) break;
+            ++local;
             tcgen05_fence_after();
             const uint32_t d0 = lane_addr + buf * acc_cols;
             if constexpr (MODE == QKV_ROPE_BF16)
@@ -1525,7 +1545,7 @@ static FerrisEpilogueAct g_launch_act = {0, 0.0f, 0.0f};
 // The persistent token-major kernel for a long step (T >= 128 tokens; output rows aligned for 16-byte stores).
 static int run_tokens_m(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                         int ldx, int ldw, int ldo, int rows_w, int up_row_offset, const RopeEpilogue* rope,
-                        cudaStream_t s) {
+                        cudaStream_t s, const int* tile_expert = nullptr, int expert_rows = 0) {
     const int accs = mode == SWIGLU_BF16 ? 2 : 1;
     const int elt = (mode == STORE_F32 || mode == ACCUM_F32) ? 4 : 2;
     sm_count();
@@ -1562,6 +1582,8 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
     q.up_row_offset = up_row_offset;
     q.status = ferris_status_ptr();
     q.rope = rope ? *rope : RopeEpilogue{};
+    q.tile_expert = tile_expert;
+    q.expert_rows = expert_rows;
     CUtensorMap mx, mw;
     int rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, PT_BLOCK_M, BLOCK_K);
     if (rc != FERRIS_OK) return rc;
@@ -1583,6 +1605,29 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
         case SWIGLU_BF16: return launch_pt<SWIGLU_BF16>(mx, mw, mo, q, ctas, smem, s);
         default: return launch_pt<QKV_ROPE_BF16>(mx, mw, mo, q, ctas, smem, s);
     }
+}
+
+// One product per group of token tiles (see PTParams::tile_expert): x holds `rows` rows (a multiple of 128), sorted by
+// expert with every expert's rows filled up to whole tiles of 128; w holds the experts' matrices stacked, expert_rows
+// rows each, of which the first N (and, in SwiGLU mode, the N from up_row_offset on) meet the rows of their tiles.
+// Modes: 0 bf16 store, 1 fp32 store, 3 SwiGLU from two accumulators.  A tile whose entry is negative is skipped.
+FERRIS_API int ferris_gemm_grouped_tcgen05(const void* x, const void* w, void* out, int mode, int rows, int N, int K,
+                                           int ldx, int ldw, int ldo, int experts, int expert_rows, int up_row_offset,
+                                           const int* tile_expert, void* stream) {
+    if (rows <= 0 || N <= 0) return FERRIS_OK;
+    if (rows % PT_BLOCK_M) FERRIS_REFUSE("grouped gemm: %d rows are no multiple of %d", rows, PT_BLOCK_M);
+    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
+        FERRIS_REFUSE("grouped gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FERRIS_REFUSE("grouped gemm: operands must be 16-byte aligned");
+    if (mode != STORE_BF16 && mode != STORE_F32 && mode != SWIGLU_BF16) FERRIS_REFUSE("grouped gemm: mode %d", mode);
+    if (!tile_expert || experts <= 0 || expert_rows <= 0) FERRIS_REFUSE("grouped gemm: no experts");
+    if ((mode == SWIGLU_BF16 ? up_row_offset + N : N) > expert_rows || up_row_offset < 0)
+        FERRIS_REFUSE("grouped gemm: %d outputs (+%d) from %d rows an expert", N, up_row_offset, expert_rows);
+    const int elt = mode == STORE_F32 ? 4 : 2;
+    if (ldo < N || ((size_t)ldo * elt) % 16 || ((uintptr_t)out & 15)) FERRIS_REFUSE("grouped gemm: output rows must start on 16 bytes");
+    g_launch_act = FerrisEpilogueAct{0, 0.0f, 0.0f};
+    return run_tokens_m(x, w, nullptr, out, mode, rows, N, K, ldx, ldw, ldo, experts * expert_rows, up_row_offset, nullptr,
+                        (cudaStream_t)stream, tile_expert, expert_rows);
 }
 
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,

@@ -10,7 +10,10 @@
 // Two ways through the experts.  Token-major (steps of few tokens, and the 32-bit path): a block per (token, chosen
 // expert) and slab of the expert's rows; the token's row stands in shared memory as fp32 and every warp forms whole
 // dot products with 16-byte loads of the weights, so a weight is read once per token that uses it and nothing is
-// gathered or scattered.  Expert-major (long steps, bf16): see moe_grouped.cu.
+// gathered or scattered.  Expert-major (long steps, bf16): the (token, expert) pairs are sorted by expert, every
+// expert's rows filled up to whole tiles of 128, the tokens' rows gathered in that order, and two tensor-core products
+// run over the tiles, each tile against its own expert's weights (ferris_gemm_grouped_tcgen05); a last pass adds every
+// token's results, in the order of its choices, into the residual rows.  The kernels here sort, gather and add.
 #include <math.h>
 
 #include "common.cuh"
@@ -115,8 +118,8 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T* x, int ldx, co
 // act[(t, s), j] = silu(Wg_e[j] . y_t) * (Wu_e[j] . y_t) for e = ids[t, s]; a block per (t, s) and slab of `slab` rows j.
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, const T* __restrict__ gate,
-                                                          const T* __restrict__ up, const int* ids, T* __restrict__ act,
-                                                          int width, int ff, int top, int slab) {
+                                                          const T* __restrict__ up, size_t expert_stride, const int* ids,
+                                                          T* __restrict__ act, int width, int ff, int top, int slab) {
     extern __shared__ __align__(16) float xs[];  // the token's row
     pdl_wait();
     pdl_launch_dependents();
@@ -125,8 +128,8 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, c
     const T* xr = x + (size_t)t * ldx;
     for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_float(xr[i]);
     __syncthreads();
-    const T* g = gate + (size_t)e * ff * width;
-    const T* u = up + (size_t)e * ff * width;
+    const T* g = gate + (size_t)e * expert_stride;
+    const T* u = up + (size_t)e * expert_stride;
     const bool vec = rows_vectorise(g, width) && rows_vectorise(u, width);
     const int j0 = blockIdx.y * slab, j1 = min(ff, j0 + slab);
     for (int j = j0 + warp; j < j1; j += 4) {
@@ -167,7 +170,130 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
     }
 }
 
+// ------------------------------------------------------------------------------------------ expert-major: sort
+// One block.  pos[pair] = the row of pair (t, s) in the sorted order; row_token[row] = its token, or -1 for a row that
+// only fills a tile up; tile_expert[tile] = the expert of the tile's rows, or -1 beyond the last row.
+constexpr int MOE_TILE = 128;
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* ids, int* pos, int* row_token, int* tile_expert,
+                                                        int pairs, int top, int experts, int max_rows) {
+    __shared__ int count[MOE_MAX_EXPERTS];
+    __shared__ int first[MOE_MAX_EXPERTS + 1];
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_token[r] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) pos[i] = atomicAdd(&count[ids[i]], 1);  // its rank, for now
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            first[e] = at;
+            at += (count[e] + MOE_TILE - 1) / MOE_TILE * MOE_TILE;
+        }
+        first[experts] = at;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int row = first[ids[i]] + pos[i];
+        pos[i] = row;
+        row_token[row] = i / top;
+    }
+    for (int tile = threadIdx.x; tile < max_rows / MOE_TILE; tile += blockDim.x) {
+        const int row = tile * MOE_TILE;
+        int e = -1;
+        if (row < first[experts]) {
+            int lo = 0, hi = experts - 1;  // the last expert whose first row is at or before this tile's
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (first[mid] <= row) lo = mid; else hi = mid - 1;
+            }
+            e = lo;
+        }
+        tile_expert[tile] = e;
+    }
+}
+
+// xs[row] = x[row_token[row]], 16 bytes a thread; rows that fill a tile up are zeroed.
+__global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* x, int ldx16, const int* row_token, uint4* xs,
+                                                         int rows, int width16) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t n = (size_t)rows * width16;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(e / width16), i = (int)(e % width16);
+        const int t = row_token[row];
+        xs[e] = t >= 0 ? x[(size_t)t * ldx16 + i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// h[t] (+)= sum_s weights[t, s] * y[pos[t, s]], in the order of the choices; four columns a thread.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ldy, const int* pos, const float* weights,
+                                                          float* h, int ldh, int tokens, int width4, int top,
+                                                          int accumulate) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t n = (size_t)tokens * width4;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(e / width4), i = (int)(e % width4);
+        float4* dst = reinterpret_cast<float4*>(h + (size_t)t * ldh) + i;
+        float4 acc = accumulate ? *dst : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s = 0; s < top; ++s) {
+            const float w = weights[(size_t)t * top + s];
+            const float4 v = reinterpret_cast<const float4*>(y + (size_t)pos[(size_t)t * top + s] * ldy)[i];
+            sum.x = fmaf(w, v.x, sum.x), sum.y = fmaf(w, v.y, sum.y), sum.z = fmaf(w, v.z, sum.z), sum.w = fmaf(w, v.w, sum.w);
+        }
+        acc.x += sum.x, acc.y += sum.y, acc.z += sum.z, acc.w += sum.w;
+        *dst = acc;
+    }
+}
+
 }  // namespace
+
+extern "C" int ferris_gemm_grouped_tcgen05(const void* x, const void* w, void* out, int mode, int rows, int N, int K,
+                                           int ldx, int ldw, int ldo, int experts, int expert_rows, int up_row_offset,
+                                           const int* tile_expert, void* stream);
+
+// Rows of the sorted order that `tokens` tokens choosing `top` of `experts` can need at most (whole tiles of 128).
+FERRIS_API int ferris_moe_sorted_rows(int tokens, int top, int experts) {
+    const long long pairs = (long long)tokens * top;
+    const long long rows = (pairs + MOE_TILE - 1) / MOE_TILE * MOE_TILE + (long long)(experts < pairs ? experts : pairs) * MOE_TILE;
+    return rows > 2147483647LL ? -1 : (int)rows;
+}
+
+// The experts of a long step in bf16.  x bf16 [tokens, width] rows ldx apart; gate_up bf16 [experts, 2 ff, width] (an
+// expert's gate rows, then its up rows); down bf16 [experts, width, ff]; ids, weights [tokens, top]; h fp32.
+// Scratch, all sized for rows = ferris_moe_sorted_rows(...): pos int32 [tokens x top], row_token int32 [rows],
+// tile_expert int32 [rows / 128], xs bf16 [rows, width], act bf16 [rows, ff], y fp32 [rows, width].
+FERRIS_API int ferris_moe_experts_grouped(const void* x, int ldx, const void* gate_up, const void* down, const int* ids,
+                                          const float* weights, float* h, int ldh, int tokens, int width, int ff, int top,
+                                          int experts, int rows, int* pos, int* row_token, int* tile_expert, void* xs,
+                                          void* act, float* y, int accumulate, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts)
+        FERRIS_REFUSE("experts: %d of %d experts", top, experts);
+    if (rows != ferris_moe_sorted_rows(tokens, top, experts)) FERRIS_REFUSE("experts: scratch for %d rows", rows);
+    if (width % 8 || ff % 8 || ldx % 8 || ldh % 4 || (((uintptr_t)x | (uintptr_t)xs | (uintptr_t)y | (uintptr_t)h) & 15))
+        FERRIS_REFUSE("experts: width %d, ff %d and the rows must be multiples of 8 elements and start on 16 bytes", width, ff);
+    cudaStream_t s = (cudaStream_t)stream;
+    ferris_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, ids, pos, row_token, tile_expert, tokens * top, top, experts,
+                  rows);
+    const size_t n16 = (size_t)rows * (width / 8);
+    const size_t want = (n16 + 255) / 256;
+    ferris_launch(moe_gather_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, s, (const uint4*)x,
+                  ldx / 8, (const int*)row_token, (uint4*)xs, rows, width / 8);
+    int rc = ferris_gemm_grouped_tcgen05(xs, gate_up, act, 3, rows, ff, width, width, width, ff, experts, 2 * ff, ff,
+                                         tile_expert, stream);
+    if (rc != FERRIS_OK) return rc;
+    rc = ferris_gemm_grouped_tcgen05(act, down, y, 1, rows, width, ff, ff, ff, width, experts, width, 0, tile_expert, stream);
+    if (rc != FERRIS_OK) return rc;
+    const size_t n4 = (size_t)tokens * (width / 4);
+    const size_t want4 = (n4 + 255) / 256;
+    ferris_launch(moe_combine_kernel, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s, (const float*)y,
+                  width, (const int*)pos, weights, h, ldh, tokens, width / 4, top, accumulate);
+    FERRIS_LAUNCH_CHECK();
+}
 
 FERRIS_API int ferris_moe_router(const void* x, int ldx, int dtype, const void* w, const float* bias, int* ids,
                                  float* weights, int tokens, int width, int experts, int top, void* stream) {
@@ -192,10 +318,12 @@ FERRIS_API int ferris_moe_router(const void* x, int ldx, int dtype, const void* 
     FERRIS_LAUNCH_CHECK();
 }
 
-// x [tokens, width] rows ldx apart; gate, up [experts, ff, width]; down [experts, width, ff]; ids int32 and weights
-// fp32 [tokens, top]; act [tokens x top, ff] (scratch, the activations' type); h fp32 rows ldh apart.
+// x [tokens, width] rows ldx apart; gate, up: expert e's [ff, width] matrices lie gate_up_stride elements after expert
+// e - 1's (two tensors, or the two halves of one [experts, 2 ff, width]); down [experts, width, ff]; ids int32 and
+// weights fp32 [tokens, top]; act [tokens x top, ff] (scratch, the activations' type); h fp32 rows ldh apart.
 FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype, const void* gate, const void* up,
-                                              const void* down, const int* ids, const float* weights, void* act, float* h,
+                                              long long gate_up_stride, const void* down, const int* ids,
+                                              const float* weights, void* act, float* h,
                                               int ldh, int tokens, int width, int ff, int top, int accumulate,
                                               void* stream) {
     if (tokens <= 0) return FERRIS_OK;
@@ -221,7 +349,7 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_gate_up_kernel<T>, smem_up)) != FERRIS_OK) return rc;        \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_down_kernel<T>, smem_down)) != FERRIS_OK) return rc;         \
         ferris_launch(moe_gate_up_kernel<T>, dim3(grid_up.x, grid_up.y, 1), dim3(128), smem_up, s, (const T*)x, ldx,      \
-                      (const T*)gate, (const T*)up, ids, (T*)act, width, ff, top, slab_up);                                    \
+                      (const T*)gate, (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, top, slab_up);                                    \
         ferris_launch(moe_down_kernel<T>, grid_down, dim3(128), smem_down, s, (const T*)act, (const T*)down, ids, weights, \
                       h, ldh, width, ff, top, slab_down, accumulate);                                                     \
     } while (0)

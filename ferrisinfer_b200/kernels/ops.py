@@ -1384,28 +1384,59 @@ def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
                                     _ptr(weights), _c_int(T), _c_int(W), _c_int(E), _c_int(top), _stream()), "router")
 
 
-def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
-                weights: torch.Tensor, h: torch.Tensor, workspace=None, accumulate: bool = True):
-    """h (+)= sum over a row's chosen experts of weight x down_e (silu(gate_e x) * (up_e x)).  gate, up [E, ff, W],
-    down [E, W, ff] in x's type; ids int32 and weights fp32 [T, top]; h fp32 [T, W]."""
+MOE_GROUPED_MIN_TOKENS = 17  # from here on (bf16) the experts' rows are sorted by expert and meet tensor-core tiles
+
+
+def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                h: torch.Tensor, workspace=None, accumulate: bool = True, grouped: Optional[bool] = None):
+    """h (+)= sum over a row's chosen experts of weight x down_e (silu(gate_e x) * (up_e x)).  gate_up [E, 2 ff, W] (an
+    expert's gate rows, then its up rows), down [E, W, ff] in x's type; ids int32 and weights fp32 [T, top]; h fp32
+    [T, W].  Steps of few tokens and the 32-bit path: a block per (token, chosen expert), weights read by whole dot
+    products.  Longer steps in bf16 (``grouped``; None = decide by size and alignment): the pairs sorted by expert, two
+    tensor-core products over tiles that each meet their own expert's weights, and a pass that adds a token's results
+    in the order of its choices."""
     T, W, ldx = _rows(x, "experts input")
     T2, W2, ldh = _rows(h, "experts output")
-    _need(gate, "gate matrices", x.dtype)
-    _need(up, "up matrices", x.dtype)
+    _need(gate_up, "gate and up matrices", x.dtype)
     _need(down, "down matrices", x.dtype)
     _need(ids, "expert ids", torch.int32)
     _need(weights, "expert weights", torch.float32)
-    E, ff = gate.shape[0], gate.shape[1]
+    E, ff = gate_up.shape[0], gate_up.shape[1] // 2
     top = ids.shape[1]
-    if (gate.shape != (E, ff, W) or up.shape != (E, ff, W) or down.shape != (E, W, ff) or (T2, W2) != (T, W)
-            or h.dtype != torch.float32 or ids.shape != (T, top) or weights.shape != (T, top)):
-        raise KernelError(f"experts: x {tuple(x.shape)}, gate {tuple(gate.shape)}, down {tuple(down.shape)}, ids {tuple(ids.shape)}")
-    act = workspace.get("moe_act", (T * top, ff), x.dtype) if workspace is not None else \
-        torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
-    _check(_lib().ferris_moe_experts_token_major(_ptr(x), _c_int(ldx), _c_int(_dt(x, "experts")), _ptr(gate), _ptr(up),
-                                                 _ptr(down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(h), _c_int(ldh),
-                                                 _c_int(T), _c_int(W), _c_int(ff), _c_int(top),
-                                                 _c_int(1 if accumulate else 0), _stream()), "experts", 2)
+    if (gate_up.shape != (E, 2 * ff, W) or down.shape != (E, W, ff) or (T2, W2) != (T, W) or h.dtype != torch.float32
+            or ids.shape != (T, top) or weights.shape != (T, top)):
+        raise KernelError(f"experts: x {tuple(x.shape)}, gate/up {tuple(gate_up.shape)}, down {tuple(down.shape)}, "
+                          f"ids {tuple(ids.shape)}")
+    get = (lambda name, shape, dtype: workspace.get(name, shape, dtype)) if workspace is not None else \
+        (lambda name, shape, dtype: torch.empty(shape, dtype=dtype, device=x.device))
+    can_group = (x.dtype == torch.bfloat16 and W % 8 == 0 and ff % 8 == 0 and ldx % 8 == 0 and ldh % 4 == 0
+                 and x.data_ptr() % 16 == 0 and h.data_ptr() % 16 == 0)
+    if grouped is None:
+        grouped = can_group and T >= MOE_GROUPED_MIN_TOKENS
+    if grouped:
+        if not can_group:
+            raise KernelError("experts: the sorted form takes bf16 rows of multiples of 8 elements that start on 16 bytes")
+        rows = _lib().ferris_moe_sorted_rows(_c_int(T), _c_int(top), _c_int(E))
+        if rows <= 0:
+            raise KernelError(f"experts: {T} tokens x {top} choices are more than one launch takes")
+        pos = get("moe_pos", (T * top,), torch.int32)
+        row_token = get("moe_row_token", (rows,), torch.int32)
+        tile_expert = get("moe_tile_expert", (rows // 128,), torch.int32)
+        xs = get("moe_sorted_rows", (rows, W), x.dtype)
+        act = get("moe_sorted_act", (rows, ff), x.dtype)
+        y = get("moe_sorted_out", (rows, W), torch.float32)
+        _check(_lib().ferris_moe_experts_grouped(_ptr(x), _c_int(ldx), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights),
+                                                 _ptr(h), _c_int(ldh), _c_int(T), _c_int(W), _c_int(ff), _c_int(top),
+                                                 _c_int(E), _c_int(rows), _ptr(pos), _ptr(row_token), _ptr(tile_expert),
+                                                 _ptr(xs), _ptr(act), _ptr(y), _c_int(1 if accumulate else 0), _stream()),
+               "experts (sorted)", 5)
+        return
+    act = get("moe_act", (T * top, ff), x.dtype)
+    up = gate_up[:, ff:, :]
+    _check(_lib().ferris_moe_experts_token_major(_ptr(x), _c_int(ldx), _c_int(_dt(x, "experts")), _ptr(gate_up), _ptr(up),
+                                                 ctypes.c_longlong(2 * ff * W), _ptr(down), _ptr(ids), _ptr(weights),
+                                                 _ptr(act), _ptr(h), _c_int(ldh), _c_int(T), _c_int(W), _c_int(ff),
+                                                 _c_int(top), _c_int(1 if accumulate else 0), _stream()), "experts", 2)
 
 
 def kernel_status() -> int:

@@ -97,8 +97,8 @@ class MixtureOfExperts(FeedForward):
     Router: z = W_r y + b_r in fp32 sums; the ``top`` largest z (the lowest index among equals); the weights are the
     softmax over those alone.  Experts have no biases.  Tensors under the prefix: ``router`` [experts, H],
     ``router.b`` [experts], and for expert i ``e<i>.gate`` / ``e<i>.up`` [ff, H], ``e<i>.down`` [H, ff]; on the device
-    the experts' matrices are stacked ([experts, ff, H] and [experts, H, ff]) so that kernels address an expert by
-    its index."""
+    the experts' matrices are stacked ([experts, 2 ff, H], an expert's gate rows before its up rows, and
+    [experts, H, ff]) so that kernels address an expert by its index."""
 
     graph_safe = True
     can_overwrite = True
@@ -111,7 +111,7 @@ class MixtureOfExperts(FeedForward):
         if not (1 <= self.top <= self.experts):
             raise ValueError(f"{self.top} of {self.experts} experts cannot be chosen")
         self._names = (router_name, router_bias_name, expert_prefix, gate_name, up_name, down_name)
-        self.router = self.router_bias = self.gate = self.up = self.down = None
+        self.router = self.router_bias = self.gate_up = self.down = None
 
     def _expert(self, prefix, e, which):
         return f"{prefix}.{self._names[2]}{e}.{which}"
@@ -129,8 +129,8 @@ class MixtureOfExperts(FeedForward):
 
     def bind(self, tensors, prefix):
         r, rb, _, g, u, d = self._names
-        self.gate = torch.stack([tensors.pop(self._expert(prefix, e, g)) for e in range(self.experts)]).contiguous()
-        self.up = torch.stack([tensors.pop(self._expert(prefix, e, u)) for e in range(self.experts)]).contiguous()
+        self.gate_up = torch.stack([torch.cat([tensors.pop(self._expert(prefix, e, g)), tensors.pop(self._expert(prefix, e, u))])
+                                    for e in range(self.experts)]).contiguous()
         self.down = torch.stack([tensors.pop(self._expert(prefix, e, d)) for e in range(self.experts)]).contiguous()
         self.router, self.router_bias = tensors[f"{prefix}.{r}"], tensors[f"{prefix}.{rb}"]
 
@@ -139,7 +139,7 @@ class MixtureOfExperts(FeedForward):
         ids = ctx.workspace.get("moe_ids", (T, self.top), torch.int32)
         weights = ctx.workspace.get("moe_weights", (T, self.top), torch.float32)
         ops.moe_router(x, self.router, self.router_bias, ids, weights, self.top)
-        ops.moe_experts(x, self.gate, self.up, self.down, ids, weights, h, ctx.workspace, accumulate=accumulate)
+        ops.moe_experts(x, self.gate_up, self.down, ids, weights, h, ctx.workspace, accumulate=accumulate)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -320,11 +320,27 @@ def test_router_takes_the_lowest_index_among_equals(device):
     assert ids.cpu().tolist() == [[1, 2, 4, 0]] * 2
 
 
-@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("dtype,grouped", [(F32, False), (BF16, False), (BF16, True)])
 @pytest.mark.parametrize("T,W,ff,E,top", [(1, 40, 24, 5, 1), (9, 44, 36, 12, 3), (70, 64, 96, 3, 3), (300, 128, 64, 8, 2),
-                                           (17, 256, 200, 6, 4)])
-def test_experts_against_the_plain_mixture(device, T, W, ff, E, top, dtype):
-    """Router and experts together through the part, adding into the residual rows and replacing them."""
+                                           (17, 256, 200, 6, 4), (700, 256, 384, 16, 4), (130, 64, 72, 40, 1)])
+def test_experts_against_the_plain_mixture(device, T, W, ff, E, top, dtype, grouped):
+    """Router and experts together through the part, adding into the residual rows and replacing them; token by token
+    (a block per token and expert) and sorted by expert (tensor-core tiles that each meet their own expert's weights:
+    experts without a token, with a few, with several tiles of them)."""
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.feed_forward import MixtureOfExperts
+
+    if grouped and (W % 8 or ff % 8):
+        pytest.skip("rows of no multiple of 8 elements go token by token")
+    was = ops.MOE_GROUPED_MIN_TOKENS
+    ops.MOE_GROUPED_MIN_TOKENS = 1 if grouped else 1 << 30
+    try:
+        _experts_against_the_plain_mixture(device, T, W, ff, E, top, dtype)
+    finally:
+        ops.MOE_GROUPED_MIN_TOKENS = was
+
+
+def _experts_against_the_plain_mixture(device, T, W, ff, E, top, dtype):
     from ferrisinfer_b200.parts.feed_forward import MixtureOfExperts
 
     torch.manual_seed(T + W)
