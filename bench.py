@@ -556,9 +556,9 @@ def main() -> int:
                     help="instead of the measurement: the Kugilix decoder beside the Qwen2 decoder at equal layer sizes "
                          "(names of bench_designs.SIZES, with commas): prefill and decode through the step function, and "
                          "the Kugilix design's own kernels alone; prints one JSON line of its own")
-    ap.add_argument("--design", default="kugilix", choices=["kugilix", "nusudra"],
-                    help="with --designs: which design is set beside the others (kugilix: beside Qwen2; nusudra: beside "
-                         "Kugilix and Qwen2, with its own kernels alone as well)")
+    ap.add_argument("--design", default="kugilix", choices=["kugilix", "nusudra", "netinex"],
+                    help="with --designs: which design is set beside the others (kugilix: beside Qwen2; nusudra or "
+                         "netinex: beside Kugilix and Qwen2, with its own kernels alone as well)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

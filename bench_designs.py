@@ -1,7 +1,7 @@
 """Designs side by side at equal layer sizes: the Kugilix decoder beside the Qwen2 dense decoder, or (``design`` =
-"nusudra") the Nusudra decoder beside both, random weights.
+"nusudra" / "netinex") the Nusudra or the Netinex decoder beside both, random weights.
 
-Called by ``bench.py --designs [--design nusudra]``.  For each of a few sizes that resemble a real model's layers it measures, through
+Called by ``bench.py --designs [--design nusudra|netinex]``.  For each of a few sizes that resemble a real model's layers it measures, through
 the step function, the prefill of one prompt and decode steps at two batch sizes for both designs, and times the
 kernels that only the Kugilix design has (decayed linear attention, the windowed attention with slopes, the short
 convolution, the norms in groups, the gated norm, the activation) alone, with what they reach of the measured copy
@@ -76,6 +76,35 @@ def nusudra_config(s: dict) -> dict:
               for i in range(kugilix_runs(s))]
     return {"architecture": "Nusudra", "vocab": VOCAB, "width": s["width"], "embedding": {"scale": math.sqrt(s["width"])},
             "norm": {"eps": 1e-6}, "streams": 4, "layers": layers}
+
+
+EXPERTS, TOP = 8, 2
+
+
+def netinex_expert_ff(s: dict) -> int:
+    """An expert's inner size such that the ``TOP`` experts a token uses hold as many weights as the Kugilix model's
+    plain feed-forward (two matrices of ff against TOP x three), in multiples of 64."""
+    return max(64, (2 * s["ff"]) // (3 * TOP) // 64 * 64)
+
+
+def netinex_config(s: dict) -> dict:
+    """As many layers as the Kugilix model has layer runs, in its order (an attention, two retentions, ...); the same
+    width, heads, head size; chunks as long as the other designs' window; ``TOP`` of ``EXPERTS`` gated experts that
+    together hold the weights of the plain feed-forward."""
+    H, G, d = s["heads"], s["kv_heads"], s["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": netinex_expert_ff(s)}, "router": {"experts": EXPERTS, "top": TOP}}
+    att = {"type": "attention",
+           "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 1.0 / math.sqrt(d), "mask": {"size": WINDOW},
+                     "rot": {"base": 10000.0, "dims": d,
+                             "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
+           "mlp": mlp}
+    ret = {"type": "retention",
+           "mixer": {"heads": H, "dim": d, "vdim": d, "rot": {"base": 1000000.0, "dims": d},
+                     "decay": [round(1.0 - 2.0 ** (-2 - 6 * h / H), 6) for h in range(H)]},
+           "mlp": mlp}
+    order = [att, ret, ret]
+    return {"architecture": "Netinex", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [order[i % 3] for i in range(kugilix_runs(s))]}
 
 
 def _timed(fn, flush, warmup=3, iters=5, reps=1):
@@ -321,10 +350,137 @@ def nusudra_kernel_numbers(s: dict, peaks: dict) -> dict:
     return out
 
 
+def netinex_kernel_numbers(s: dict, peaks: dict) -> dict:
+    """The Netinex design's own kernels alone at the layer sizes ``s``, measured as ``kernel_numbers`` measures; the
+    experts beside the plain feed-forward of as many weights per token (``bf16``: FLOPs over the measured cuBLAS rate)."""
+    import torch
+    from types import SimpleNamespace
+
+    from ferrisinfer_b200.engine.workspace import Workspace
+    from ferrisinfer_b200.kernels import ops
+
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.zeros(96 << 20, dtype=torch.float32, device=dev)  # 384 MB
+    W, H, G, d, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    hbm = peaks["hbm_gbs"] * 1e9
+    tensor = peaks["bf16_tflops"] * 1e12
+    ws = Workspace(dev)
+    out = {}
+
+    def ctx_of(q_lens, start):
+        S = len(q_lens)
+        q_start = [0]
+        for n in q_lens:
+            q_start.append(q_start[-1] + n)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, max_q_len=max(q_lens), workspace=ws,
+                               max_kv_len=start + max(q_lens),
+                               token_seq=i32([i for i in range(S) for _ in range(q_lens[i])]),
+                               positions=i32([start + j for i in range(S) for j in range(q_lens[i])]),
+                               seq_q_start=i32(q_start), seq_start_pos=i32([start] * S), seq_state_slot=i32(list(range(S))))
+
+    def record(name, seconds, bytes_=None, flops=None, tensor_flops=None):
+        e = {"us": round(seconds * 1e6, 1)}
+        if bytes_ is not None:
+            e["GBps"] = round(bytes_ / seconds / 1e9, 1)
+            e["frac_hbm"] = round(bytes_ / seconds / hbm, 3)
+        if flops is not None:
+            e["TFLOPs_fp32"] = round(flops / seconds / 1e12, 2)
+            e["frac_fp32_nominal"] = round(flops / seconds / (FP32_NOMINAL_TFLOPS * 1e12), 3)
+        if tensor_flops is not None:
+            e["TFLOPs_bf16"] = round(tensor_flops / seconds / 1e12, 1)
+            e["frac_bf16_measured"] = round(tensor_flops / seconds / tensor, 3)
+        out[name] = e
+
+    # ---- retention: the decayed linear attention with q and k rotated and k scaled on the way in
+    freq = torch.exp(-math.log(1e6) * torch.arange(d // 2, device=dev, dtype=torch.float32) * 2 / d)
+    table = ops.RotaryTable(freq, d, interleaved=False)
+    for name, q_lens in (("retention_decode_b64", [1] * 64), ("retention_prefill_2048", [2048])):
+        T, S = sum(q_lens), len(q_lens)
+        proj = torch.randn(T, 4 * H * d, device=dev).to(bf)
+        state = torch.zeros(S + 1, H, d, d, device=dev)
+        o = torch.empty(T, H * d, device=dev)
+        decay = torch.full((H,), 0.97, device=dev)
+        ctx = ctx_of(q_lens, 7)
+        t = _timed(lambda: ops.linear_attention(proj, (0, H * d, 2 * H * d), o, state, decay, ctx, H, d, d, silu=False,
+                                                rotary=table, k_scale=d ** -0.5), flush)
+        moved = 2 * S * H * d * d * 4 + T * 3 * H * d * 2 + T * H * d * 4
+        record(name, t, bytes_=moved, flops=4.0 * T * H * d * d)
+    # ---- attention within chunks, the values read from the raw keys' rows; and the kernel ahead of it
+    itab = ops.RotaryTable(freq, d, interleaved=True, magnitude=1.1)
+    for name, batch, q_len, ctx_len in (("decode_b64", 64, 1, 2047), ("prefill_2048", 1, 2048, 0)):
+        T = batch * q_len
+        pages_each = (ctx_len + q_len + 15) // 16
+        k = torch.randn(batch * pages_each + 1, G, 16, d, device=dev).to(bf)
+        v = torch.randn_like(k)
+        tables = torch.arange(batch * pages_each, dtype=torch.int32, device=dev).view(batch, pages_each)
+        qk = torch.randn(T, (H + G) * d, device=dev).to(bf)
+        o = torch.empty(T, H * d, dtype=bf, device=dev)
+        ctx = ctx_of([q_len] * batch, ctx_len)
+        t = _timed(lambda: ops.paged_attention_simt(qk, o, k, v, tables, ctx.token_seq, ctx.positions, H, G, d, 0,
+                                                    1.0 / math.sqrt(d), v_head_dim=d, max_q_len=q_len,
+                                                    max_kv_len=ctx_len + q_len, workspace=ws, chunk=WINDOW), flush)
+        keys = sum((ctx_len + j) % WINDOW + 1 for j in range(q_len)) * batch
+        record(f"chunk_attention_{name}", t, flops=4.0 * keys * H * d,
+               bytes_=batch * G * (ctx_len % WINDOW + 1) * 2 * d * 2 + T * H * d * 4 if q_len == 1 else None)
+        slots = (tables[ctx.token_seq.long(), (ctx.positions // 16).long()] * 16 + ctx.positions % 16).int()
+        qn, kn = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev)
+        t = _timed(lambda: ops.qk_norm_rotary_cache_write(qk, ctx, slots, k, v, H, G, d, d, qn, kn, 1e-6, itab,
+                                                          values_from_keys=True), flush, reps=10)
+        record(f"qk_norm_rotary_{name}", t, bytes_=T * (2 * H * d + 3 * G * d) * 2)
+    # ---- row-wise kernels of a long step and of a decode step
+    for tag, T in (("2048", 2048), ("b64", 64)):
+        reps = 10 if T <= 64 else 1
+        h = torch.randn(T, W, device=dev)
+        w1, b1, alpha = torch.ones(W, device=dev), torch.zeros(W, device=dev), torch.full((1,), 0.7, device=dev)
+        a = torch.empty(T, W, dtype=bf, device=dev)
+        t = _timed(lambda: ops.dynamic_tanh(h, w1, b1, alpha, a), flush, reps=reps)
+        record(f"dynamic_tanh_{tag}", t, bytes_=T * W * (4 + 2))
+        o = torch.randn(T, H * d, device=dev)
+        g = torch.randn(T, H * d, device=dev).to(bf)
+        y = torch.empty(T, H * d, dtype=bf, device=dev)
+        one = torch.ones(1, device=dev)
+        t = _timed(lambda: ops.gated_group_norm(o, g, one, 1e-6, y, group=d, gate_kind="silu"), flush, reps=reps)
+        record(f"head_norm_silu_gate_{tag}", t, bytes_=T * H * d * (4 + 2 + 2))
+        logits = torch.randn(T, VOCAB, device=dev)
+        t = _timed(lambda: ops.softcap_(logits, 30.0), flush, reps=reps)
+        record(f"softcap_{tag}", t, bytes_=T * VOCAB * 8)
+    # ---- the experts beside the plain feed-forward of as many weights per token
+    eff = netinex_expert_ff(s)
+    gate_up = (torch.randn(EXPERTS, 2 * eff, W, device=dev) / math.sqrt(W)).to(bf)
+    down = (torch.randn(EXPERTS, W, eff, device=dev) / math.sqrt(eff)).to(bf)
+    router = torch.randn(EXPERTS, W, device=dev).to(bf)
+    rb = torch.zeros(EXPERTS, device=dev)
+    w_up = (torch.randn(ff, W, device=dev) / math.sqrt(W)).to(bf)
+    w_down = (torch.randn(W, ff, device=dev) / math.sqrt(ff)).to(bf)
+    for tag, T in (("b8", 8), ("b64", 64), ("2048", 2048)):
+        x = torch.randn(T, W, device=dev).to(bf)
+        hrow = torch.zeros(T, W, device=dev)
+        ids = torch.empty(T, TOP, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, TOP, device=dev)
+        t = _timed(lambda: ops.moe_router(x, router, rb, ids, wts, TOP), flush, reps=10)
+        record(f"router_{tag}", t, bytes_=T * W * 2 + EXPERTS * W * 2)
+        distinct = int(torch.unique(ids).numel())
+        t = _timed(lambda: ops.moe_experts(x, gate_up, down, ids, wts, hrow, ws, accumulate=True), flush)
+        record(f"experts_{tag}", t, bytes_=distinct * 3 * W * eff * 2 + T * W * (2 + 8),
+               tensor_flops=2.0 * T * TOP * 3 * W * eff)
+        out[f"experts_{tag}"]["distinct_experts"] = distinct
+        act = torch.empty(T, ff, dtype=bf, device=dev)
+
+        def dense():
+            ops.gemm_activation(x, w_up, act, "silu")
+            ops.gemm(act, w_down, None, hrow, accumulate=True)
+
+        t = _timed(dense, flush)
+        record(f"dense_feed_forward_{tag}", t, bytes_=2 * W * ff * 2 + T * W * (2 + 8), tensor_flops=2.0 * T * 2 * W * ff)
+    return out
+
+
 def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, sizes=("small", "1B-like"), context=2048,
         prompt=2048, batches=(8, 64), kernels_at="1B-like", design="kugilix") -> dict:
     """``build_engine(cfg, batch, context, extra_tokens)``, ``time_decode`` and ``time_prefill`` are bench.py's.
-    ``design`` "kugilix": that design beside Qwen2; "nusudra": that design beside both."""
+    ``design`` "kugilix": that design beside Qwen2; "nusudra" or "netinex": that design beside both."""
     import torch
 
     result = {"context": context, "prompt_tokens": prompt, "window": WINDOW, "sizes": {}}
@@ -334,6 +490,8 @@ def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, size
         designs = (("kugilix", kugilix_config(s)), ("qwen2", qwen2_config(s)))
         if design == "nusudra":
             designs = (("nusudra", nusudra_config(s)),) + designs
+        if design == "netinex":
+            designs = (("netinex", netinex_config(s)),) + designs
         for design_name, cfg in designs:
             numbers = {}
             engine = build_engine(cfg, 1, context, extra_tokens=prompt)
@@ -357,4 +515,8 @@ def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, size
         result["kernels"] = {"at": kernels_at, **kernel_numbers(SIZES[kernels_at], peaks)}
         if design == "nusudra":
             result["kernels_nusudra"] = {"at": kernels_at, **nusudra_kernel_numbers(SIZES[kernels_at], peaks)}
+        if design == "netinex":
+            result["kernels_netinex"] = {"at": kernels_at, "expert_ff": netinex_expert_ff(SIZES[kernels_at]),
+                                         "experts": EXPERTS, "top": TOP,
+                                         **netinex_kernel_numbers(SIZES[kernels_at], peaks)}
     return result
