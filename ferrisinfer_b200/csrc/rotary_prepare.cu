@@ -11,7 +11,14 @@
 //
 // Rows: [nh d | nkv d | nkv dv unless values_from_keys].  Everything is computed in fp32 (position x frequency as one
 // fp32 product, sincosf in full precision); one block per token.
+//
+// Two kernels.  The paired one (even head sizes and row strides, rows that start on a pair): a token's cosines and
+// sines are formed once in shared memory and serve all its heads, both sums of squares come out of one pass and one
+// reduction, and every thread loads, norms, rotates and stores two neighbouring elements at a time (in the
+// interleaved layout a pair that rotates together is one such load).  The general one takes every other geometry
+// element by element.
 #include <math.h>
+#include <stdint.h>
 
 #include "common.cuh"
 
@@ -91,6 +98,111 @@ __global__ void __launch_bounds__(128) qk_norm_rotary_cache_write_kernel(
     }
 }
 
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const bf16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// Two sums over a block at once; every thread gets both.  `scratch` holds 66 floats.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a), b = warp_sum(b);
+    if (lane == 0) scratch[warp] = a, scratch[32 + warp] = b;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    if (warp == 0) {
+        float x = lane < nwarps ? scratch[lane] : 0.0f, y = lane < nwarps ? scratch[32 + lane] : 0.0f;
+        x = warp_sum(x), y = warp_sum(y);
+        if (lane == 0) scratch[64] = x, scratch[65] = y;
+    }
+    __syncthreads();
+    return make_float2(scratch[64], scratch[65]);
+}
+
+// d, dv, ld, nq, nk even; rows and caches start on a pair of elements.  Dynamic shared memory: `rotary` floats (the
+// token's cosines, then its sines, both times mag).
+template <typename T, bool INTERLEAVED>
+__global__ void __launch_bounds__(256) qk_norm_rotary_cache_write_paired_kernel(
+    T* qkv, int ld, const int* __restrict__ positions, const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int nh, int nkv, int d, int dv, int page_size, const float* __restrict__ q_weight,
+    const float* __restrict__ k_weight, float eps, const float* __restrict__ freq, int rotary, float mag,
+    int values_from_keys, int write_kv) {
+    extern __shared__ float cs[];
+    __shared__ float scratch[66];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int half = rotary >> 1;
+    const int pos = positions[t];
+    for (int f = threadIdx.x; f < half; f += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * freq[f], &s, &c);
+        cs[f] = c * mag, cs[half + f] = s * mag;
+    }
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    T* row = qkv + (size_t)t * ld;
+    const int nq = nh * d, nk = nkv * d;
+    float sq = 0.0f, sk = 0.0f;
+    if (q_weight)
+        for (int e = 2 * threadIdx.x; e < nq; e += 2 * blockDim.x) {
+            const float2 v = load2(row + e);
+            sq = fmaf(v.x, v.x, sq), sq = fmaf(v.y, v.y, sq);
+        }
+    if (k_weight)
+        for (int e = 2 * threadIdx.x; e < nk; e += 2 * blockDim.x) {
+            const float2 v = load2(row + nq + e);
+            sk = fmaf(v.x, v.x, sk), sk = fmaf(v.y, v.y, sk);
+        }
+    const float2 sums = block_sum2(sq, sk, scratch);  // also: the table is written
+    const float inv_q = q_weight ? 1.0f / sqrtf(sums.x / (float)nq + eps) : 1.0f;
+    const float inv_k = k_weight ? 1.0f / sqrtf(sums.y / (float)nk + eps) : 1.0f;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int in_page = slot >= 0 ? slot % page_size : 0;
+    if (slot >= 0) {
+        const T* vrow = values_from_keys ? row + nq : row + nq + nk;
+        for (int e = 2 * threadIdx.x; e < nkv * dv; e += 2 * blockDim.x) {
+            const int h = e / dv, i = e - h * dv;
+            const float2 v = load2(vrow + e);
+            store2(v_cache + (((size_t)page * nkv + h) * page_size + in_page) * dv + i, v.x, v.y);
+        }
+    }
+    const int last = slot >= 0 ? nq + nk : nq;
+    const int per_head = d >> 1;  // items of a head: its rotating pairs, then its other elements two by two
+    for (int item = threadIdx.x; item < (last >> 1); item += blockDim.x) {
+        const int head = item / per_head, j = item - head * per_head;
+        const bool is_q = head < nh;
+        const int h = is_q ? head : head - nh;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? q_weight : k_weight;
+        const T* src = row + (size_t)head * d;
+        const float* wh = w ? w + (size_t)h * d : nullptr;
+        T* dst = is_q ? row + (size_t)head * d : k_cache + (((size_t)page * nkv + h) * page_size + in_page) * d;
+        if (j >= half) {  // two elements that pass
+            const int i = rotary + 2 * (j - half);
+            float2 x = load2(src + i);
+            if (w) x.x = (x.x * inv) * wh[i], x.y = (x.y * inv) * wh[i + 1];
+            store2(dst + i, x.x, x.y);
+            continue;
+        }
+        const float c = cs[j], s = cs[half + j];
+        if (INTERLEAVED) {
+            const int i = 2 * j;
+            float2 x = load2(src + i);
+            if (w) x.x = (x.x * inv) * wh[i], x.y = (x.y * inv) * wh[i + 1];
+            store2(dst + i, x.x * c - x.y * s, x.y * c + x.x * s);
+        } else {
+            float u = to_float(src[j]), v = to_float(src[j + half]);
+            if (w) u = (u * inv) * wh[j], v = (v * inv) * wh[j + half];
+            dst[j] = from_float<T>(u * c - v * s);
+            dst[j + half] = from_float<T>(v * c + u * s);
+        }
+    }
+}
+
 }  // namespace
 
 FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, const int* positions,
@@ -108,6 +220,24 @@ FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, c
     if (ld < (nh + nkv) * d + (values_from_keys ? 0 : nkv * dv)) FERRIS_REFUSE("qk norm + rotation: rows of %d are too short", ld);
     if (write_kv && (!slot_mapping || !k_cache || !v_cache)) FERRIS_REFUSE("qk norm + rotation: no cache to write");
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t elem = dtype == FERRIS_F32 ? 4 : 2;
+    const bool paired = !((d | dv | ld) & 1) && (uintptr_t)qkv % (2 * elem) == 0 && (uintptr_t)k_cache % (2 * elem) == 0 &&
+                        (uintptr_t)v_cache % (2 * elem) == 0 && ((uintptr_t)q_weight | (uintptr_t)k_weight) % 8 == 0 &&
+                        (dtype == FERRIS_F32 || dtype == FERRIS_BF16);
+    if (paired) {
+        const size_t smem = (size_t)rotary * sizeof(float);
+#define FERRIS_PAIRED(T, I)                                                                                              \
+    ferris_launch(qk_norm_rotary_cache_write_paired_kernel<T, I>, dim3(tokens), dim3(256), smem, s, (T*)qkv, ld, positions, \
+                  slot_mapping, (T*)k_cache, (T*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps, freq, rotary,  \
+                  mag, values_from_keys, write_kv)
+        if (dtype == FERRIS_F32) {
+            if (interleaved) FERRIS_PAIRED(float, true); else FERRIS_PAIRED(float, false);
+        } else {
+            if (interleaved) FERRIS_PAIRED(bf16, true); else FERRIS_PAIRED(bf16, false);
+        }
+#undef FERRIS_PAIRED
+        FERRIS_LAUNCH_CHECK();
+    }
     if (dtype == FERRIS_F32)
         ferris_launch(qk_norm_rotary_cache_write_kernel<float>, dim3(tokens), dim3(128), 0, s, (float*)qkv, ld, positions,
                       slot_mapping, (float*)k_cache, (float*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps,

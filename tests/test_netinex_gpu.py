@@ -173,6 +173,53 @@ def test_chunked_attention_one_key_stands_out_at_each_edge(device, chunk, last, 
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("layout", ["interleaved", "half"])
+@pytest.mark.parametrize("nh,nkv,d,dims,normed,from_keys", [(4, 2, 32, 32, True, True), (3, 1, 40, 24, True, True),
+                                                             (2, 2, 15, 6, True, True), (5, 5, 9, 8, False, False),
+                                                             (16, 4, 128, 128, True, True), (2, 1, 64, 0, True, False),
+                                                             (1, 1, 6, 2, False, True)])
+def test_norm_over_the_projection_rotation_and_cache_write(device, nh, nkv, d, dims, normed, from_keys, layout, dtype):
+    """The kernel between the q/k product and attention alone, in its paired form (even head sizes) and its general one
+    (odd ones), both pair layouts, part of a head rotating, with and without the norm, values taken from the keys or
+    from a third part of the row: the queries left in the row, the keys and values found in their cache slots."""
+    ops = _ops()
+    torch.manual_seed(nh * 100 + d)
+    T, ps, eps = 37, 16, 1e-5
+    rot = cases.rotation(dims, 700.0, (4.0, 64, 8.0, 2.0)) if dims else None
+    f, mag = plain.frequencies(rot)
+    width = (nh + nkv) * d + (0 if from_keys else nkv * d)
+    rows = torch.randn(T, width).to(dtype)
+    qw, kw = 1.0 + 0.2 * torch.randn(nh * d), 1.0 + 0.2 * torch.randn(nkv * d)
+    positions = [3 + 5 * t for t in range(T)]
+    x = rows.double()
+    q, k = x[:, :nh * d], x[:, nh * d:(nh + nkv) * d]
+    values = k if from_keys else x[:, (nh + nkv) * d:]
+    if normed:
+        q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * qw.double()
+        k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * kw.double()
+    q = plain.rotate(q.view(T, nh, d), positions, rot, layout).reshape(T, nh * d)
+    k = plain.rotate(k.view(T, nkv, d), positions, rot, layout).reshape(T, nkv * d)
+    kc, vc, _, slots = paged(device, dtype, T, nkv, d, ps, [2, 0, 1])
+    ctx = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=device))
+    table = None if not dims else ops.RotaryTable(torch.tensor(f, dtype=F32, device=device), dims, layout == "interleaved", mag)
+    dev_rows = rows.to(device)
+    ops.qk_norm_rotary_cache_write(dev_rows, ctx, slots, kc, vc, nh, nkv, d, d, qw.to(device) if normed else None,
+                                   kw.to(device) if normed else None, eps, table, values_from_keys=from_keys)
+    tol = tol_of(dtype)
+    assert torch.allclose(dev_rows[:, :nh * d].cpu().double(), q, **tol)
+    slot = slots.cpu().long()
+    got_k = kc.cpu().double().permute(0, 2, 1, 3).reshape(-1, nkv * d)[slot]
+    got_v = vc.cpu().double().permute(0, 2, 1, 3).reshape(-1, nkv * d)[slot]
+    assert torch.allclose(got_k, k, **tol)
+    assert torch.equal(got_v, values)
+    # without a cache to write, the queries alone change
+    again = rows.to(device)
+    ops.qk_norm_rotary_cache_write(again, ctx, None, None, None, nh, nkv, d, d, qw.to(device) if normed else None,
+                                   kw.to(device) if normed else None, eps, table, values_from_keys=from_keys, write_kv=False)
+    assert torch.equal(again[:, :nh * d], dev_rows[:, :nh * d]) and torch.equal(again[:, nh * d:].cpu(), rows[:, nh * d:])
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("nh,nkv,d,rot,chunk", [(4, 2, 32, cases.rotation(32, 10000.0, (4.0, 64, 8.0, 2.0)), 48),
                                                   (3, 1, 40, cases.rotation(24, 100.0), 21),
                                                   (6, 6, 16, None, 16), (2, 1, 128, cases.rotation(128, 1e6, (2.0, 32, 4.0, 1.0)), None),
