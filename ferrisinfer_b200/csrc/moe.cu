@@ -7,10 +7,14 @@
 //
 // The experts' matrices lie stacked: gate and up as [experts, ff, width] each, down as [experts, width, ff].
 //
-// Two ways through the experts.  Token-major (steps of few tokens, and the 32-bit path): a block per (token, chosen
-// expert) and slab of the expert's rows; the token's row stands in shared memory as fp32 and every warp forms whole
-// dot products with 16-byte loads of the weights, so a weight is read once per token that uses it and nothing is
-// gathered or scattered.  Expert-major (long steps, bf16): the (token, expert) pairs are sorted by expert, every
+// Three ways through the experts.  Token-major (a single choice; the 32-bit path of long steps): a block per (token, chosen expert) and
+// slab of the expert's rows; the token's row stands in shared memory as fp32 and every warp forms whole dot products
+// with 16-byte loads of the weights, so a weight is read once per token that uses it and nothing is gathered or
+// scattered.  Expert-major for few tokens (decode steps): a block per (expert, slab of rows) finds the tokens that
+// chose its expert, holds four of their rows in shared memory at a time and forms the same dot products for all four
+// from one pass over the weight rows, which every lane streams through shared memory with asynchronous 16-byte copies
+// a few steps ahead; a last pass adds every token's results in the order of its choices.  Both give a token the same
+// bits.  Expert-major (long steps, bf16): the (token, expert) pairs are sorted by expert, every
 // expert's rows filled up to whole tiles of 128, the tokens' rows gathered in that order, and two tensor-core products
 // run over the tiles, each tile against its own expert's weights (ferris_gemm_grouped_tcgen05); a last pass adds every
 // token's results, in the order of its choices, into the residual rows.  The kernels here sort, gather and add.
@@ -57,35 +61,213 @@ __device__ __forceinline__ float dot_row(const bf16* __restrict__ w, const float
     }
     return warp_sum(acc);
 }
+// 16 bytes of a weight row as fp32: four elements of float, eight of bf16
+__device__ __forceinline__ void load_chunk(const float* w, int i, float (&f)[4]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(w) + i);
+    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w;
+}
+__device__ __forceinline__ void load_chunk(const bf16* w, int i, float (&f)[8]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(w) + i);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 v = __bfloat1622float2(p[q]);
+        f[2 * q] = v.x, f[2 * q + 1] = v.y;
+    }
+}
+// R weight rows against M rows in shared memory (fp32, `xstride` apart): the R loads of a step are in flight together
+// and serve all M rows.  Every sum is formed in the order of dot_row, so a result depends on neither R nor M.
+template <int R, int M, typename T>
+__device__ __forceinline__ void dot_tile(const T* const (&w)[R], const float* xs, int xstride, int n, int lane, bool vec,
+                                         float (&out)[R][M]) {
+    constexpr int C = 16 / (int)sizeof(T);
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    if (vec) {
+        for (int i = lane; i < n / C; i += 32) {
+            float f[R][C];
+#pragma unroll
+            for (int r = 0; r < R; ++r) load_chunk(w[r], i, f[r]);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+#pragma unroll
+                for (int q = 0; q < C; q += 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(xs + (size_t)m * xstride + C * i + q);
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+                        acc[r][m] = fmaf(f[r][q], x.x, fmaf(f[r][q + 1], x.y, fmaf(f[r][q + 2], x.z, fmaf(f[r][q + 3], x.w, acc[r][m]))));
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float a = to_float(w[r][i]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) acc[r][m] = fmaf(a, xs[(size_t)m * xstride + i], acc[r][m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) out[r][m] = warp_sum(acc[r][m]);
+}
+// The same sums with the weights streamed through shared memory: every lane copies its own 16-byte pieces of the R
+// rows asynchronously into slots that only it reads back (so nothing but its own copy groups orders them), FEW_STAGES
+// steps ahead.  The bytes in flight are then bounded by shared memory, not by registers.  Needs the 16-byte form (vec).
+constexpr int FEW_STAGES = 4;
+constexpr int FEW_RING_BYTES = FEW_STAGES * 4 * 512;  // per warp: stages x up to 4 rows x 32 lanes x 16 bytes
+__device__ __forceinline__ void copy16_async(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void chunk_to_float(const uint4& a, float (&f)[4], const float*) {
+    f[0] = __uint_as_float(a.x), f[1] = __uint_as_float(a.y), f[2] = __uint_as_float(a.z), f[3] = __uint_as_float(a.w);
+}
+__device__ __forceinline__ void chunk_to_float(const uint4& a, float (&f)[8], const bf16*) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 v = __bfloat1622float2(p[q]);
+        f[2 * q] = v.x, f[2 * q + 1] = v.y;
+    }
+}
+template <int R, int M, typename T>
+__device__ __forceinline__ void dot_tile_streamed(const T* const (&w)[R], const float* xs, int xstride, int n, int lane,
+                                                  uint4* ring, float (&out)[R][M]) {
+    constexpr int C = 16 / (int)sizeof(T);
+    static_assert(R <= 4, "a warp's slots hold four rows");
+    const int chunks = n / C;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    uint4* mine = ring + lane;  // slot (stage, r) at mine[(stage * 4 + r) * 32]
+#pragma unroll
+    for (int st = 0; st < FEW_STAGES; ++st) {
+        const int i = lane + 32 * st;
+        if (i < chunks) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) copy16_async(mine + (st * 4 + r) * 32, reinterpret_cast<const uint4*>(w[r]) + i);
+        }
+        copy_commit();
+    }
+    int st = 0;
+    for (int i = lane; i < chunks; i += 32) {
+        copy_wait<FEW_STAGES - 1>();
+        float f[R][C];
+#pragma unroll
+        for (int r = 0; r < R; ++r) chunk_to_float(mine[(st * 4 + r) * 32], f[r], (const T*)nullptr);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+#pragma unroll
+            for (int q = 0; q < C; q += 4) {
+                const float4 x = *reinterpret_cast<const float4*>(xs + (size_t)m * xstride + C * i + q);
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    acc[r][m] = fmaf(f[r][q], x.x, fmaf(f[r][q + 1], x.y, fmaf(f[r][q + 2], x.z, fmaf(f[r][q + 3], x.w, acc[r][m]))));
+            }
+        }
+        const int next = i + 32 * FEW_STAGES;  // the slot is read: it takes the piece FEW_STAGES steps on
+        if (next < chunks) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) copy16_async(mine + (st * 4 + r) * 32, reinterpret_cast<const uint4*>(w[r]) + next);
+        }
+        copy_commit();
+        st = st + 1 == FEW_STAGES ? 0 : st + 1;
+    }
+    copy_wait<0>();
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) out[r][m] = warp_sum(acc[r][m]);
+}
+// streamed where the rows take 16-byte pieces, else element by element
+template <int R, int M, typename T>
+__device__ __forceinline__ void dot_tile_few(const T* const (&w)[R], const float* xs, int xstride, int n, int lane, bool vec,
+                                             uint4* ring, float (&out)[R][M]) {
+    if (vec)
+        dot_tile_streamed<R, M>(w, xs, xstride, n, lane, ring, out);
+    else
+        dot_tile<R, M>(w, xs, xstride, n, lane, false, out);
+}
+template <int R, typename T>
+__device__ __forceinline__ void dot_rows(const T* const (&w)[R], const float* xs, int n, int lane, bool vec, float (&out)[R]) {
+    float d[R][1];
+    dot_tile<R, 1>(w, xs, 0, n, lane, vec, d);
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = d[r][0];
+}
 template <typename T>
 __device__ __forceinline__ bool rows_vectorise(const T* w, int n) {
     return n % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)w & 15) == 0;
 }
 
-// ------------------------------------------------------------------------------------------ router
-// A warp per token: logits of all experts (fp32), then `top` rounds of "the largest that is left".
+// dst[0..n) (shared memory, fp32, 16-byte aligned) = src[0..n), by threads `me` of `threads`; 16-byte loads, several in
+// flight, where the row allows them.  The source is not written while the kernel runs.
 template <typename T>
+__device__ __forceinline__ void stage_row(float* dst, const T* src, int n, int me, int threads) {
+    constexpr int C = 16 / (int)sizeof(T);
+    if (n % C == 0 && ((uintptr_t)src & 15) == 0) {
+#pragma unroll 4
+        for (int i = me; i < n / C; i += threads) {
+            float f[C];
+            load_chunk(src, i, f);
+#pragma unroll
+            for (int q = 0; q < C; q += 4)
+                *reinterpret_cast<float4*>(dst + C * i + q) = make_float4(f[q], f[q + 1], f[q + 2], f[q + 3]);
+        }
+    } else {
+#pragma unroll 4
+        for (int i = me; i < n; i += threads) dst[i] = to_float(src[i]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ router
+// Logits of all experts (fp32), then `top` rounds of "the largest that is left".  A warp per token; in steps of few
+// tokens (BLOCK) a block per token, whose four warps share the experts' dot products (each formed by one warp in the
+// same order either way, so a token's logits do not depend on the form) and whose first warp then chooses.
+template <typename T, bool BLOCK>
 __global__ void __launch_bounds__(128) moe_router_kernel(const T* x, int ldx, const T* __restrict__ w,
                                                          const float* __restrict__ bias, int* __restrict__ ids,
                                                          float* __restrict__ weights, int tokens, int width, int experts,
                                                          int top) {
-    extern __shared__ __align__(16) float smem[];  // per warp: the token's row (width) and its logits (experts)
+    extern __shared__ __align__(16) float smem[];  // per warp (per block): the token's row (width) and its logits (experts)
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * 4 + warp;
+    const int t = BLOCK ? blockIdx.x : blockIdx.x * 4 + warp;
     if (t >= tokens) return;
-    float* xs = smem + (size_t)warp * (width + experts);
+    float* xs = smem + (BLOCK ? 0 : (size_t)warp * ((width + experts + 3) & ~3));  // every warp's row starts on 16 bytes
     float* z = xs + width;
     const T* xr = x + (size_t)t * ldx;
-    for (int i = lane; i < width; i += 32) xs[i] = to_float(xr[i]);
-    __syncwarp();
+    if (BLOCK) {
+        stage_row(xs, xr, width, threadIdx.x, blockDim.x);
+        __syncthreads();
+    } else {
+        stage_row(xs, xr, width, lane, 32);
+        __syncwarp();
+    }
     const bool vec = rows_vectorise(w, width) && ((uintptr_t)xs & 15) == 0;
-    for (int e = 0; e < experts; ++e) {
+    for (int e = BLOCK ? warp : 0; e < experts; e += BLOCK ? 4 : 1) {
         const float dot = dot_row(w + (size_t)e * width, xs, width, lane, vec);
         if (lane == 0) z[e] = dot + (bias ? bias[e] : 0.0f);
     }
-    __syncwarp();
+    if (BLOCK) {
+        __syncthreads();
+        if (warp) return;
+    } else {
+        __syncwarp();
+    }
     float chosen_z = 0.0f, first_z = 0.0f, sum = 0.0f;  // lane s keeps the s-th choice
     int chosen = 0;
     for (int s = 0; s < top; ++s) {
@@ -126,16 +308,29 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, c
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pair = blockIdx.x, t = pair / top, e = ids[pair];
     const T* xr = x + (size_t)t * ldx;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_float(xr[i]);
+    stage_row(xs, xr, width, threadIdx.x, blockDim.x);
     __syncthreads();
     const T* g = gate + (size_t)e * expert_stride;
     const T* u = up + (size_t)e * expert_stride;
     const bool vec = rows_vectorise(g, width) && rows_vectorise(u, width);
     const int j0 = blockIdx.y * slab, j1 = min(ff, j0 + slab);
-    for (int j = j0 + warp; j < j1; j += 4) {
-        const float a = dot_row(g + (size_t)j * width, xs, width, lane, vec);
-        const float b = dot_row(u + (size_t)j * width, xs, width, lane, vec);
-        if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>((a / (1.0f + expf(-a))) * b);
+    // a warp takes rows j and j + 4 of both matrices at a time: four weight rows in flight for one read of the token's row
+    for (int j = j0 + warp; j < j1; j += 8) {
+        if (j + 4 < j1) {
+            const T* const rows[4] = {g + (size_t)j * width, u + (size_t)j * width, g + (size_t)(j + 4) * width,
+                                      u + (size_t)(j + 4) * width};
+            float d[4];
+            dot_rows<4>(rows, xs, width, lane, vec, d);
+            if (lane == 0) {
+                act[(size_t)pair * ff + j] = from_float<T>((d[0] / (1.0f + expf(-d[0]))) * d[1]);
+                act[(size_t)pair * ff + j + 4] = from_float<T>((d[2] / (1.0f + expf(-d[2]))) * d[3]);
+            }
+        } else {
+            const T* const rows[2] = {g + (size_t)j * width, u + (size_t)j * width};
+            float d[2];
+            dot_rows<2>(rows, xs, width, lane, vec, d);
+            if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>((d[0] / (1.0f + expf(-d[0]))) * d[1]);
+        }
     }
 }
 
@@ -152,20 +347,185 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x;
     const T* ar = act + (size_t)t * top * ff;
-    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = to_float(ar[i]);
+    stage_row(as, ar, top * ff, threadIdx.x, blockDim.x);
     if (threadIdx.x < top) es[threadIdx.x] = ids[(size_t)t * top + threadIdx.x], ws[threadIdx.x] = weights[(size_t)t * top + threadIdx.x];
     __syncthreads();
     const bool vec = rows_vectorise(down, ff) && (ff * sizeof(float)) % 16 == 0;
     const int c0 = blockIdx.y * slab, c1 = min(width, c0 + slab);
-    for (int c = c0 + warp; c < c1; c += 4) {
-        float sum = 0.0f;
+    // a warp takes columns c, c + 4, c + 8 and c + 12 at a time: four weight rows in flight for one read of the activations
+    for (int c = c0 + warp; c < c1; c += 16) {
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const int n = min(4, (c1 - c + 3) / 4);
         for (int s = 0; s < top; ++s) {
-            const T* row = down + ((size_t)es[s] * width + c) * ff;
-            sum = fmaf(ws[s], dot_row(row, as + (size_t)s * ff, ff, lane, vec), sum);
+            const T* first = down + ((size_t)es[s] * width + c) * ff;
+            const float* a = as + (size_t)s * ff;
+            if (n == 4) {
+                const T* const rows[4] = {first, first + (size_t)4 * ff, first + (size_t)8 * ff, first + (size_t)12 * ff};
+                float d[4];
+                dot_rows<4>(rows, a, ff, lane, vec, d);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) sum[r] = fmaf(ws[s], d[r], sum[r]);
+            } else {
+                for (int r = 0; r < n; ++r) sum[r] = fmaf(ws[s], dot_row(first + (size_t)4 * r * ff, a, ff, lane, vec), sum[r]);
+            }
         }
         if (lane == 0) {
-            float* dst = h + (size_t)t * ldh + c;
-            *dst = accumulate ? *dst + sum : sum;
+            for (int r = 0; r < n; ++r) {
+                float* dst = h + (size_t)t * ldh + c + 4 * r;
+                *dst = accumulate ? *dst + sum[r] : sum[r];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ expert-major, few tokens
+// Steps of few tokens with the weights read once per expert instead of once per (token, expert): a block per (expert,
+// slab of rows) lists the pairs that chose its expert (in the order of the pairs), takes their tokens' rows into shared
+// memory four at a time and forms every weight row's dot products with all four from one load of the row.  Blocks of
+// experts that nobody chose return at once.  Every sum is formed as in the token-major kernels, bit for bit.
+constexpr int MOE_FEW_ROWS = 4;       // token rows in shared memory at a time: a warp stages a row
+constexpr int MOE_FEW_MAX_PAIRS = 1024;
+
+// list[0..n) = the pairs whose expert is e, ascending; returns n (to every thread)
+__device__ __forceinline__ int pairs_of_expert(const int* ids, int pairs, int e, int* list, int* count) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int n = 0;
+        for (int base = 0; base < pairs; base += 32) {
+            const int p = base + lane;
+            const bool mine = p < pairs && ids[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) list[n + __popc(m & ((1u << lane) - 1u))] = p;
+            n += __popc(m);
+        }
+        if (lane == 0) *count = n;
+    }
+    __syncthreads();
+    return *count;
+}
+
+template <typename T, int M>
+__device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float* xs, int width, int ff, int j0, int j1,
+                                             const int* pair, T* __restrict__ act, int lane, int warp, bool vec,
+                                             uint4* ring) {
+    for (int j = j0 + warp; j < j1; j += 8) {
+        if (j + 4 < j1) {
+            const T* const rows[4] = {g + (size_t)j * width, u + (size_t)j * width, g + (size_t)(j + 4) * width,
+                                      u + (size_t)(j + 4) * width};
+            float d[4][M];
+            dot_tile_few<4, M>(rows, xs, width, width, lane, vec, ring, d);
+            if (lane == 0) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    act[(size_t)pair[m] * ff + j] = from_float<T>((d[0][m] / (1.0f + expf(-d[0][m]))) * d[1][m]);
+                    act[(size_t)pair[m] * ff + j + 4] = from_float<T>((d[2][m] / (1.0f + expf(-d[2][m]))) * d[3][m]);
+                }
+            }
+        } else {
+            const T* const rows[2] = {g + (size_t)j * width, u + (size_t)j * width};
+            float d[2][M];
+            dot_tile_few<2, M>(rows, xs, width, width, lane, vec, ring, d);
+            if (lane == 0) {
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+                    act[(size_t)pair[m] * ff + j] = from_float<T>((d[0][m] / (1.0f + expf(-d[0][m]))) * d[1][m]);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gate_up_few_kernel(const T* x, int ldx, const T* __restrict__ gate,
+                                                              const T* __restrict__ up, size_t expert_stride, const int* ids,
+                                                              T* __restrict__ act, int width, int ff, int pairs, int top,
+                                                              int slab) {
+    extern __shared__ __align__(16) float dyn[];  // every warp's slots for weights in flight, then MOE_FEW_ROWS token rows
+    __shared__ int list[MOE_FEW_MAX_PAIRS];
+    __shared__ int count;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint4* ring = reinterpret_cast<uint4*>(dyn) + warp * (FEW_RING_BYTES / 16);
+    float* xs = dyn + 4 * (FEW_RING_BYTES / 4);
+    const int e = blockIdx.x;
+    const int n = pairs_of_expert(ids, pairs, e, list, &count);
+    if (n == 0) return;
+    const T* g = gate + (size_t)e * expert_stride;
+    const T* u = up + (size_t)e * expert_stride;
+    const bool vec = rows_vectorise(g, width) && rows_vectorise(u, width);
+    const int j0 = blockIdx.y * slab, j1 = min(ff, j0 + slab);
+    for (int first = 0; first < n; first += MOE_FEW_ROWS) {
+        const int m = min(MOE_FEW_ROWS, n - first);
+        if (first) __syncthreads();  // the rows before are done with
+        // a warp a row, so that the rows' loads are in flight together
+        if (warp < m) stage_row(xs + (size_t)warp * width, x + (size_t)(list[first + warp] / top) * ldx, width, lane, 32);
+        __syncthreads();
+        const int* pair = list + first;
+        switch (m) {
+            case 1: gate_up_rows<T, 1>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
+            case 2: gate_up_rows<T, 2>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
+            case 3: gate_up_rows<T, 3>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
+            default: gate_up_rows<T, 4>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
+        }
+    }
+}
+
+template <typename T, int M>
+__device__ __forceinline__ void down_rows(const T* d, const float* as, int width, int ff, int c0, int c1, const int* pair,
+                                          float* __restrict__ y, int lane, int warp, bool vec, uint4* ring) {
+    for (int c = c0 + warp; c < c1; c += 16) {
+        const int n = min(4, (c1 - c + 3) / 4);
+        float sum[4][M];
+        if (n == 4) {
+            const T* const rows[4] = {d + (size_t)c * ff, d + (size_t)(c + 4) * ff, d + (size_t)(c + 8) * ff,
+                                      d + (size_t)(c + 12) * ff};
+            dot_tile_few<4, M>(rows, as, ff, ff, lane, vec, ring, sum);
+        } else {
+            for (int r = 0; r < n; ++r) {
+                const T* const row[1] = {d + (size_t)(c + 4 * r) * ff};
+                float one[1][M];
+                dot_tile_few<1, M>(row, as, ff, ff, lane, vec, ring, one);
+#pragma unroll
+                for (int m = 0; m < M; ++m) sum[r][m] = one[0][m];
+            }
+        }
+        if (lane == 0) {
+            for (int r = 0; r < n; ++r)
+#pragma unroll
+                for (int m = 0; m < M; ++m) y[(size_t)pair[m] * width + c + 4 * r] = sum[r][m];
+        }
+    }
+}
+
+// y[pair, c] = Wd_e[c] . act[pair] for the pairs of expert e; a block per (expert, slab of columns)
+template <typename T>
+__global__ void __launch_bounds__(128) moe_down_few_kernel(const T* act, const T* __restrict__ down, const int* ids,
+                                                           float* __restrict__ y, int width, int ff, int pairs, int slab) {
+    extern __shared__ __align__(16) float dyn[];  // every warp's slots for weights in flight, then MOE_FEW_ROWS rows of activations
+    __shared__ int list[MOE_FEW_MAX_PAIRS];
+    __shared__ int count;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint4* ring = reinterpret_cast<uint4*>(dyn) + warp * (FEW_RING_BYTES / 16);
+    float* as = dyn + 4 * (FEW_RING_BYTES / 4);
+    const int e = blockIdx.x;
+    const int n = pairs_of_expert(ids, pairs, e, list, &count);
+    if (n == 0) return;
+    const T* d = down + (size_t)e * width * ff;
+    const bool vec = rows_vectorise(d, ff) && (ff * sizeof(float)) % 16 == 0;
+    const int c0 = blockIdx.y * slab, c1 = min(width, c0 + slab);
+    for (int first = 0; first < n; first += MOE_FEW_ROWS) {
+        const int m = min(MOE_FEW_ROWS, n - first);
+        if (first) __syncthreads();
+        if (warp < m) stage_row(as + (size_t)warp * ff, act + (size_t)list[first + warp] * ff, ff, lane, 32);
+        __syncthreads();
+        const int* pair = list + first;
+        switch (m) {
+            case 1: down_rows<T, 1>(d, as, width, ff, c0, c1, pair, y, lane, warp, vec, ring); break;
+            case 2: down_rows<T, 2>(d, as, width, ff, c0, c1, pair, y, lane, warp, vec, ring); break;
+            case 3: down_rows<T, 3>(d, as, width, ff, c0, c1, pair, y, lane, warp, vec, ring); break;
+            default: down_rows<T, 4>(d, as, width, ff, c0, c1, pair, y, lane, warp, vec, ring); break;
         }
     }
 }
@@ -227,7 +587,8 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* x, int ldx
     }
 }
 
-// h[t] (+)= sum_s weights[t, s] * y[pos[t, s]], in the order of the choices; four columns a thread.
+// h[t] (+)= sum_s weights[t, s] * y[pos[t, s]] (without pos: y[t x top + s]), in the order of the choices; four columns
+// a thread.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ldy, const int* pos, const float* weights,
                                                           float* h, int ldh, int tokens, int width4, int top,
                                                           int accumulate) {
@@ -241,7 +602,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ld
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         for (int s = 0; s < top; ++s) {
             const float w = weights[(size_t)t * top + s];
-            const float4 v = reinterpret_cast<const float4*>(y + (size_t)pos[(size_t)t * top + s] * ldy)[i];
+            const size_t row = pos ? (size_t)pos[(size_t)t * top + s] : (size_t)t * top + s;
+            const float4 v = reinterpret_cast<const float4*>(y + row * ldy)[i];
             sum.x = fmaf(w, v.x, sum.x), sum.y = fmaf(w, v.y, sum.y), sum.z = fmaf(w, v.z, sum.z), sum.w = fmaf(w, v.w, sum.w);
         }
         acc.x += sum.x, acc.y += sum.y, acc.z += sum.z, acc.w += sum.w;
@@ -301,33 +663,78 @@ FERRIS_API int ferris_moe_router(const void* x, int ldx, int dtype, const void* 
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || top > MOE_MAX_TOP || width <= 0)
         FERRIS_REFUSE("router: %d experts (at most %d), %d chosen (at most %d), width %d", experts, MOE_MAX_EXPERTS, top,
                       MOE_MAX_TOP, width);
-    const size_t smem = 4 * (size_t)(width + experts) * sizeof(float);
+    const bool per_block = tokens <= 148 * 2;  // few tokens: a block each, so that more warps share the work
+    const size_t smem = (per_block ? 1 : 4) * (size_t)((width + experts + 3) & ~3) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((tokens + 3) / 4), block(128);
+    const dim3 grid(per_block ? tokens : (tokens + 3) / 4), block(128);
     int rc;
+#define FERRIS_ROUTER_RUN(T, B)                                                                                          \
+    do {                                                                                                                 \
+        if ((rc = ferris_allow_dynamic_smem((const void*)moe_router_kernel<T, B>, smem)) != FERRIS_OK) return rc;        \
+        ferris_launch(moe_router_kernel<T, B>, grid, block, smem, s, (const T*)x, ldx, (const T*)w, bias, ids, weights,  \
+                      tokens, width, experts, top);                                                                      \
+    } while (0)
     if (dtype == FERRIS_F32) {
-        if ((rc = ferris_allow_dynamic_smem((const void*)moe_router_kernel<float>, smem)) != FERRIS_OK) return rc;
-        ferris_launch(moe_router_kernel<float>, grid, block, smem, s, (const float*)x, ldx, (const float*)w, bias, ids,
-                      weights, tokens, width, experts, top);
+        if (per_block) FERRIS_ROUTER_RUN(float, true); else FERRIS_ROUTER_RUN(float, false);
     } else if (dtype == FERRIS_BF16) {
-        if ((rc = ferris_allow_dynamic_smem((const void*)moe_router_kernel<bf16>, smem)) != FERRIS_OK) return rc;
-        ferris_launch(moe_router_kernel<bf16>, grid, block, smem, s, (const bf16*)x, ldx, (const bf16*)w, bias, ids, weights,
-                      tokens, width, experts, top);
+        if (per_block) FERRIS_ROUTER_RUN(bf16, true); else FERRIS_ROUTER_RUN(bf16, false);
     } else
         FERRIS_REFUSE("router: unknown dtype %d", dtype);
+#undef FERRIS_ROUTER_RUN
     FERRIS_LAUNCH_CHECK();
 }
 
 // x [tokens, width] rows ldx apart; gate, up: expert e's [ff, width] matrices lie gate_up_stride elements after expert
 // e - 1's (two tensors, or the two halves of one [experts, 2 ff, width]); down [experts, width, ff]; ids int32 and
 // weights fp32 [tokens, top]; act [tokens x top, ff] (scratch, the activations' type); h fp32 rows ldh apart.
+// With y (scratch, fp32 [tokens x top, width]), `experts` and few enough tokens the weights are read once per expert
+// (the expert-major kernels for few tokens and the adding pass); the sums are the same bit for bit either way.
 FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype, const void* gate, const void* up,
                                               long long gate_up_stride, const void* down, const int* ids,
                                               const float* weights, void* act, float* h,
                                               int ldh, int tokens, int width, int ff, int top, int accumulate,
-                                              void* stream) {
+                                              float* y, int experts, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || top > MOE_MAX_TOP) FERRIS_REFUSE("experts: width %d, ff %d, %d chosen", width, ff, top);
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("experts: unknown dtype %d", dtype);
+    const size_t few_up = 4 * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * width * sizeof(float);
+    const size_t few_down = 4 * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * ff * sizeof(float);
+    if (y && experts > 0 && (long long)tokens * top <= MOE_FEW_MAX_PAIRS && tokens * top > 1 && width % 4 == 0 &&
+        ldh % 4 == 0 && (((uintptr_t)y | (uintptr_t)h) & 15) == 0 && few_up <= 200 * 1024 && few_down <= 200 * 1024 &&
+        experts <= 65535) {
+        cudaStream_t s = (cudaStream_t)stream;
+        const int pairs = tokens * top, busy = experts < pairs ? experts : pairs;
+        // slabs of rows: as large as still fills the SMs a few times over with the experts that can be busy (a block
+        // takes its tokens' rows into shared memory once per slab, so small slabs cost reads of their own)
+        auto slab_of = [busy](int rows) {
+            int slab = 64;
+            while (slab > 8 && (long long)busy * ((rows + slab - 1) / slab) < 148 * 6) slab >>= 1;
+            return slab;
+        };
+        const int slab_up = slab_of(ff), slab_down = slab_of(width) < 16 ? 16 : slab_of(width);
+        const dim3 grid_up(experts, (ff + slab_up - 1) / slab_up), grid_down(experts, (width + slab_down - 1) / slab_down);
+        if (grid_up.y > 65535 || grid_down.y > 65535) FERRIS_REFUSE("experts: too many slabs");
+        int rc;
+#define FERRIS_MOE_FEW(T)                                                                                                 \
+    do {                                                                                                                  \
+        if ((rc = ferris_allow_dynamic_smem((const void*)moe_gate_up_few_kernel<T>, few_up)) != FERRIS_OK) return rc;     \
+        if ((rc = ferris_allow_dynamic_smem((const void*)moe_down_few_kernel<T>, few_down)) != FERRIS_OK) return rc;      \
+        ferris_launch(moe_gate_up_few_kernel<T>, grid_up, dim3(128), few_up, s, (const T*)x, ldx, (const T*)gate,         \
+                      (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, pairs, top, slab_up);                \
+        ferris_launch(moe_down_few_kernel<T>, grid_down, dim3(128), few_down, s, (const T*)act, (const T*)down, ids, y,   \
+                      width, ff, pairs, slab_down);                                                                       \
+    } while (0)
+        if (dtype == FERRIS_F32)
+            FERRIS_MOE_FEW(float);
+        else
+            FERRIS_MOE_FEW(bf16);
+#undef FERRIS_MOE_FEW
+        const size_t n4 = (size_t)tokens * (width / 4);
+        const size_t want4 = (n4 + 255) / 256;
+        ferris_launch(moe_combine_kernel, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s,
+                      (const float*)y, width, (const int*)nullptr, weights, h, ldh, tokens, width / 4, top, accumulate);
+        FERRIS_LAUNCH_CHECK();
+    }
     const size_t smem_up = (size_t)width * sizeof(float), smem_down = (size_t)top * ff * sizeof(float);
     if (smem_up > 200 * 1024 || smem_down > 200 * 1024)
         FERRIS_REFUSE("experts: a row of %d or %d x %d activations do not fit shared memory", width, top, ff);

@@ -1384,6 +1384,7 @@ def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
                                     _ptr(weights), _c_int(T), _c_int(W), _c_int(E), _c_int(top), _stream()), "router")
 
 
+MOE_FEW_MAX_PAIRS = 1024  # up to here the token-major form reads an expert's weights once for all its tokens
 MOE_GROUPED_MIN_TOKENS = 17  # from here on (bf16) the experts' rows are sorted by expert and meet tensor-core tiles
 
 
@@ -1391,8 +1392,9 @@ def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids:
                 h: torch.Tensor, workspace=None, accumulate: bool = True, grouped: Optional[bool] = None):
     """h (+)= sum over a row's chosen experts of weight x down_e (silu(gate_e x) * (up_e x)).  gate_up [E, 2 ff, W] (an
     expert's gate rows, then its up rows), down [E, W, ff] in x's type; ids int32 and weights fp32 [T, top]; h fp32
-    [T, W].  Steps of few tokens and the 32-bit path: a block per (token, chosen expert), weights read by whole dot
-    products.  Longer steps in bf16 (``grouped``; None = decide by size and alignment): the pairs sorted by expert, two
+    [T, W].  Steps of few tokens (up to MOE_FEW_MAX_PAIRS choices): a block per (expert, slab of rows) reads the weights
+    once for all tokens that chose the expert.  More choices in 32-bit: a block per (token, chosen expert).  Both form
+    whole dot products in the same order, so a token's result has the same bits.  Longer steps in bf16 (``grouped``; None = decide by size and alignment): the pairs sorted by expert, two
     tensor-core products over tiles that each meet their own expert's weights, and a pass that adds a token's results
     in the order of its choices."""
     T, W, ldx = _rows(x, "experts input")
@@ -1433,10 +1435,15 @@ def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids:
         return
     act = get("moe_act", (T * top, ff), x.dtype)
     up = gate_up[:, ff:, :]
+    # few pairs: the weights are read once per expert, the results of a pair stand in y until they are added
+    few = 1 < T * top <= MOE_FEW_MAX_PAIRS and W % 4 == 0 and ldh % 4 == 0 and h.data_ptr() % 16 == 0
+    y = get("moe_pair_out", (T * top, W), torch.float32) if few else None
     _check(_lib().ferris_moe_experts_token_major(_ptr(x), _c_int(ldx), _c_int(_dt(x, "experts")), _ptr(gate_up), _ptr(up),
                                                  ctypes.c_longlong(2 * ff * W), _ptr(down), _ptr(ids), _ptr(weights),
                                                  _ptr(act), _ptr(h), _c_int(ldh), _c_int(T), _c_int(W), _c_int(ff),
-                                                 _c_int(top), _c_int(1 if accumulate else 0), _stream()), "experts", 2)
+                                                 _c_int(top), _c_int(1 if accumulate else 0),
+                                                 _ptr(y) if few else ctypes.c_void_p(0), _c_int(E), _stream()),
+           "experts", 3 if few else 2)
 
 
 def kernel_status() -> int:

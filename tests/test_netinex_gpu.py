@@ -341,7 +341,8 @@ def test_retention_reads_a_write_from_hundreds_of_tokens_ago_through_the_rotatio
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("T,W,E,top", [(1, 40, 5, 1), (9, 44, 12, 3), (70, 64, 3, 3), (33, 256, 64, 8), (5, 72, 40, 32)])
+@pytest.mark.parametrize("T,W,E,top", [(1, 40, 5, 1), (9, 44, 12, 3), (70, 64, 3, 3), (33, 256, 64, 8), (5, 72, 40, 32),
+                                        (297, 48, 6, 6), (400, 72, 9, 2)])
 def test_router_choices_and_weights(device, T, W, E, top, dtype):
     ops = _ops()
     torch.manual_seed(T * E)
@@ -356,6 +357,11 @@ def test_router_choices_and_weights(device, T, W, E, top, dtype):
     assert torch.equal(ids.cpu().long(), order)
     want = torch.softmax(torch.gather(z, 1, order), dim=-1)
     assert torch.allclose(weights.cpu().double(), want, atol=1e-5, rtol=1e-4)
+    # a token alone (a block per token) and among hundreds (a warp per token): the same bits
+    ids1 = torch.empty(1, top, dtype=torch.int32, device=device)
+    weights1 = torch.empty(1, top, device=device)
+    ops.moe_router(x[T - 1:].to(device), wr.to(device), b.to(device), ids1, weights1, top)
+    assert torch.equal(ids1[0], ids[T - 1]) and torch.equal(weights1[0], weights[T - 1])
 
 
 def test_router_takes_the_lowest_index_among_equals(device):
@@ -410,6 +416,27 @@ def _experts_against_the_plain_mixture(device, T, W, ff, E, top, dtype):
     assert torch.allclose((h.cpu().double() - before.double())[sure], want[sure], **tol_of(dtype, 3.0))
     part.forward(y.to(device), h, ctx, accumulate=False)
     assert torch.allclose(h.cpu().double()[sure], want[sure], **tol_of(dtype, 3.0))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("W,ff", [(64, 96), (44, 36)])
+def test_experts_give_a_token_the_same_bits_alone_and_among_others(device, W, ff, dtype):
+    """One choice per token: a token alone goes through the kernels of a block per (token, expert), eleven tokens through
+    those that read an expert's weights once for all its tokens (four at a time, so some experts take several turns)."""
+    ops = _ops()
+    torch.manual_seed(W)
+    E, T = 3, 11
+    gate_up = (torch.randn(E, 2 * ff, W) / math.sqrt(W)).to(device, dtype)
+    down = (torch.randn(E, W, ff) / math.sqrt(ff)).to(device, dtype)
+    x = torch.randn(T, W).to(device, dtype)
+    ids = torch.tensor([[t % 2 * 2] for t in range(T)], dtype=torch.int32, device=device)  # expert 1 stays without a token
+    weights = torch.rand(T, 1, device=device) + 0.5
+    together = torch.zeros(T, W, device=device)
+    ops.moe_experts(x, gate_up, down, ids, weights, together, None, accumulate=False, grouped=False)
+    for t in range(T):
+        alone = torch.zeros(1, W, device=device)
+        ops.moe_experts(x[t:t + 1], gate_up, down, ids[t:t + 1], weights[t:t + 1], alone, None, accumulate=False, grouped=False)
+        assert torch.equal(alone[0], together[t]), t
 
 
 # ================================================================================================ whole models
