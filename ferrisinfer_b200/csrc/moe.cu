@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
 // experts that nobody chose return at once.  Every sum is formed as in the token-major kernels, bit for bit.
 constexpr int MOE_FEW_ROWS = 4;       // token rows in shared memory at a time: a warp stages a row
 constexpr int MOE_FEW_MAX_PAIRS = 1024;
+constexpr int FEW_WARPS = 8;          // warps a block: they share the token rows
 
 // list[0..n) = the pairs whose expert is e, ascending; returns n (to every thread)
 __device__ __forceinline__ int pairs_of_expert(const int* ids, int pairs, int e, int* list, int* count) {
@@ -408,17 +409,17 @@ template <typename T, int M>
 __device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float* xs, int width, int ff, int j0, int j1,
                                              const int* pair, T* __restrict__ act, int lane, int warp, bool vec,
                                              uint4* ring) {
-    for (int j = j0 + warp; j < j1; j += 8) {
-        if (j + 4 < j1) {
-            const T* const rows[4] = {g + (size_t)j * width, u + (size_t)j * width, g + (size_t)(j + 4) * width,
-                                      u + (size_t)(j + 4) * width};
+    for (int j = j0 + warp; j < j1; j += 2 * FEW_WARPS) {
+        if (j + FEW_WARPS < j1) {
+            const T* const rows[4] = {g + (size_t)j * width, u + (size_t)j * width, g + (size_t)(j + FEW_WARPS) * width,
+                                      u + (size_t)(j + FEW_WARPS) * width};
             float d[4][M];
             dot_tile_few<4, M>(rows, xs, width, width, lane, vec, ring, d);
             if (lane == 0) {
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     act[(size_t)pair[m] * ff + j] = from_float<T>((d[0][m] / (1.0f + expf(-d[0][m]))) * d[1][m]);
-                    act[(size_t)pair[m] * ff + j + 4] = from_float<T>((d[2][m] / (1.0f + expf(-d[2][m]))) * d[3][m]);
+                    act[(size_t)pair[m] * ff + j + FEW_WARPS] = from_float<T>((d[2][m] / (1.0f + expf(-d[2][m]))) * d[3][m]);
                 }
             }
         } else {
@@ -435,7 +436,7 @@ __device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128) moe_gate_up_few_kernel(const T* x, int ldx, const T* __restrict__ gate,
+__global__ void __launch_bounds__(32 * FEW_WARPS) moe_gate_up_few_kernel(const T* x, int ldx, const T* __restrict__ gate,
                                                               const T* __restrict__ up, size_t expert_stride, const int* ids,
                                                               T* __restrict__ act, int width, int ff, int pairs, int top,
                                                               int slab) {
@@ -446,7 +447,7 @@ __global__ void __launch_bounds__(128) moe_gate_up_few_kernel(const T* x, int ld
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint4* ring = reinterpret_cast<uint4*>(dyn) + warp * (FEW_RING_BYTES / 16);
-    float* xs = dyn + 4 * (FEW_RING_BYTES / 4);
+    float* xs = dyn + FEW_WARPS * (FEW_RING_BYTES / 4);
     const int e = blockIdx.x;
     const int n = pairs_of_expert(ids, pairs, e, list, &count);
     if (n == 0) return;
@@ -473,16 +474,16 @@ __global__ void __launch_bounds__(128) moe_gate_up_few_kernel(const T* x, int ld
 template <typename T, int M>
 __device__ __forceinline__ void down_rows(const T* d, const float* as, int width, int ff, int c0, int c1, const int* pair,
                                           float* __restrict__ y, int lane, int warp, bool vec, uint4* ring) {
-    for (int c = c0 + warp; c < c1; c += 16) {
-        const int n = min(4, (c1 - c + 3) / 4);
+    for (int c = c0 + warp; c < c1; c += 4 * FEW_WARPS) {
+        const int n = min(4, (c1 - c + FEW_WARPS - 1) / FEW_WARPS);
         float sum[4][M];
         if (n == 4) {
-            const T* const rows[4] = {d + (size_t)c * ff, d + (size_t)(c + 4) * ff, d + (size_t)(c + 8) * ff,
-                                      d + (size_t)(c + 12) * ff};
+            const T* const rows[4] = {d + (size_t)c * ff, d + (size_t)(c + FEW_WARPS) * ff, d + (size_t)(c + 2 * FEW_WARPS) * ff,
+                                      d + (size_t)(c + 3 * FEW_WARPS) * ff};
             dot_tile_few<4, M>(rows, as, ff, ff, lane, vec, ring, sum);
         } else {
             for (int r = 0; r < n; ++r) {
-                const T* const row[1] = {d + (size_t)(c + 4 * r) * ff};
+                const T* const row[1] = {d + (size_t)(c + FEW_WARPS * r) * ff};
                 float one[1][M];
                 dot_tile_few<1, M>(row, as, ff, ff, lane, vec, ring, one);
 #pragma unroll
@@ -492,14 +493,14 @@ __device__ __forceinline__ void down_rows(const T* d, const float* as, int width
         if (lane == 0) {
             for (int r = 0; r < n; ++r)
 #pragma unroll
-                for (int m = 0; m < M; ++m) y[(size_t)pair[m] * width + c + 4 * r] = sum[r][m];
+                for (int m = 0; m < M; ++m) y[(size_t)pair[m] * width + c + FEW_WARPS * r] = sum[r][m];
         }
     }
 }
 
 // y[pair, c] = Wd_e[c] . act[pair] for the pairs of expert e; a block per (expert, slab of columns)
 template <typename T>
-__global__ void __launch_bounds__(128) moe_down_few_kernel(const T* act, const T* __restrict__ down, const int* ids,
+__global__ void __launch_bounds__(32 * FEW_WARPS) moe_down_few_kernel(const T* act, const T* __restrict__ down, const int* ids,
                                                            float* __restrict__ y, int width, int ff, int pairs, int slab) {
     extern __shared__ __align__(16) float dyn[];  // every warp's slots for weights in flight, then MOE_FEW_ROWS rows of activations
     __shared__ int list[MOE_FEW_MAX_PAIRS];
@@ -508,7 +509,7 @@ __global__ void __launch_bounds__(128) moe_down_few_kernel(const T* act, const T
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint4* ring = reinterpret_cast<uint4*>(dyn) + warp * (FEW_RING_BYTES / 16);
-    float* as = dyn + 4 * (FEW_RING_BYTES / 4);
+    float* as = dyn + FEW_WARPS * (FEW_RING_BYTES / 4);
     const int e = blockIdx.x;
     const int n = pairs_of_expert(ids, pairs, e, list, &count);
     if (n == 0) return;
@@ -697,8 +698,8 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
     if (tokens <= 0) return FERRIS_OK;
     if (width <= 0 || ff <= 0 || top <= 0 || top > MOE_MAX_TOP) FERRIS_REFUSE("experts: width %d, ff %d, %d chosen", width, ff, top);
     if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("experts: unknown dtype %d", dtype);
-    const size_t few_up = 4 * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * width * sizeof(float);
-    const size_t few_down = 4 * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * ff * sizeof(float);
+    const size_t few_up = FEW_WARPS * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * width * sizeof(float);
+    const size_t few_down = FEW_WARPS * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * ff * sizeof(float);
     if (y && experts > 0 && (long long)tokens * top <= MOE_FEW_MAX_PAIRS && tokens * top > 1 && width % 4 == 0 &&
         ldh % 4 == 0 && (((uintptr_t)y | (uintptr_t)h) & 15) == 0 && few_up <= 200 * 1024 && few_down <= 200 * 1024 &&
         experts <= 65535) {
@@ -707,11 +708,11 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
         // slabs of rows: as large as still fills the SMs a few times over with the experts that can be busy (a block
         // takes its tokens' rows into shared memory once per slab, so small slabs cost reads of their own)
         auto slab_of = [busy](int rows) {
-            int slab = 64;
-            while (slab > 8 && (long long)busy * ((rows + slab - 1) / slab) < 148 * 6) slab >>= 1;
+            int slab = 128;
+            while (slab > 4 * FEW_WARPS && (long long)busy * ((rows + slab - 1) / slab) < 148 * 4) slab >>= 1;
             return slab;
         };
-        const int slab_up = slab_of(ff), slab_down = slab_of(width) < 16 ? 16 : slab_of(width);
+        const int slab_up = slab_of(ff), slab_down = slab_of(width);
         const dim3 grid_up(experts, (ff + slab_up - 1) / slab_up), grid_down(experts, (width + slab_down - 1) / slab_down);
         if (grid_up.y > 65535 || grid_down.y > 65535) FERRIS_REFUSE("experts: too many slabs");
         int rc;
@@ -719,9 +720,9 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
     do {                                                                                                                  \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_gate_up_few_kernel<T>, few_up)) != FERRIS_OK) return rc;     \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_down_few_kernel<T>, few_down)) != FERRIS_OK) return rc;      \
-        ferris_launch(moe_gate_up_few_kernel<T>, grid_up, dim3(128), few_up, s, (const T*)x, ldx, (const T*)gate,         \
+        ferris_launch(moe_gate_up_few_kernel<T>, grid_up, dim3(32 * FEW_WARPS), few_up, s, (const T*)x, ldx, (const T*)gate,         \
                       (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, pairs, top, slab_up);                \
-        ferris_launch(moe_down_few_kernel<T>, grid_down, dim3(128), few_down, s, (const T*)act, (const T*)down, ids, y,   \
+        ferris_launch(moe_down_few_kernel<T>, grid_down, dim3(32 * FEW_WARPS), few_down, s, (const T*)act, (const T*)down, ids, y,   \
                       width, ff, pairs, slab_down);                                                                       \
     } while (0)
         if (dtype == FERRIS_F32)
