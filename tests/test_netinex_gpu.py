@@ -557,6 +557,36 @@ def test_a_long_prompt_and_its_decoded_tail(device):
     check_rows(got, {"far": want}, "float32", "a long prompt and its tail")
 
 
+MID = cases.config([cases.retention_layer(8, 32, 64, cases.experts(192, 16, 4), rot=cases.rotation(32, 500000.0), seed=7),
+                    cases.attention_layer(8, 2, 80, 160, cases.experts(192, 16, 4),
+                                          rot=cases.rotation(80, 10000.0, (4.0, 1024, 32.0, 1.0))),
+                    cases.retention_layer(8, 32, 64, None, rot=cases.rotation(32, 500000.0), seed=8),
+                    cases.attention_layer(8, 2, 80, 160, cases.experts(192, 16, 4),
+                                          rot=cases.rotation(80, 10000.0, (4.0, 1024, 32.0, 1.0)))],
+                   width=256, vocab=2000, softcap=20.0)
+
+
+@functools.lru_cache(maxsize=None)
+def wider_model():
+    weights = cases.make_weights(MID, seed=99)
+    return weights, {name: cases.safe_sequence(MID, weights, n, seed)
+                     for name, n, seed in (("far", 400, 5), ("mid", 150, 6), ("short", 70, 7))}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_pages_of_64(device, dtype):
+    """Sizes nearer a real model's (a width of 256, heads of 80, four of sixteen experts, a vocabulary of 2,000) over
+    pages of 64: a prompt of 400 with its decoded tail, then three requests in portions beside single tokens over four
+    slots and just enough pages."""
+    weights, seqs = wider_model()
+    runner = make_runner(MID, weights, dtype, device, num_pages=13, page_size=64)
+    got = helpers.replay(runner, helpers.trace_tail_decoded({"far": seqs["far"][0]}, tail=40))
+    check_rows(got, {"far": seqs["far"][1]}, dtype, "a wider model: prompt and tail")
+    got = helpers.replay(runner, helpers.trace_mixed({n: ids for n, (ids, _) in seqs.items()}, seed=3))
+    check_rows(got, {n: rows for n, (_, rows) in seqs.items()}, dtype, "a wider model: mixed")
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(device, tmp_path, dtype):
     """A folder of the design through ``Engine.generate`` (scheduler, portions, sampling on the device): every token
