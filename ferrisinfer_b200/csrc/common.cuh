@@ -184,7 +184,10 @@ __device__ __forceinline__ void ferris_tl_value(int k, unsigned long long v) {
 // ferris_gemm_set_activation leaves it for the NEXT product launched through this library, which takes it (and clears
 // it) when it fills its parameters.  kind 0: none; 1: xIELU, a z^2 + z / 2 for z > 0 and b (exp(z) - 1 - z) + z / 2
 // otherwise; 2: SiLU; 3: the square of max(z, 0).  Evaluated in fp32 on the accumulator, before the one rounding to bf16.
+// Kinds from FERRIS_EPILOGUE_GATED on go with the products of two accumulators (gate and up) instead: kind -
+// FERRIS_EPILOGUE_GATED is the kind of ferris_gated_act and `a` its limit (ferris_gemm_set_gated_activation).
 // ---------------------------------------------------------------------------------------------
+#define FERRIS_EPILOGUE_GATED 16
 struct FerrisEpilogueAct {
     int kind;
     float a, b;
@@ -195,6 +198,27 @@ __device__ __forceinline__ float ferris_epilogue_act(float z, const FerrisEpilog
     if (e.kind == 2) return z / (1.0f + expf(-z));
     if (e.kind == 3) return z > 0.0f ? z * z : 0.0f;
     return z;
+}
+
+// ---------------------------------------------------------------------------------------------
+// What a gated feed-forward makes of its gate product g and its up product u, in fp32:
+//   kind 0: silu(g) u;   kind 1: gelu(g) u in the tanh form, gelu(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)));
+//   kind 2 (with a limit L): g' = min(g, L), u' = clamp(u, -L, L):  g' sigmoid(1.702 g') (u' + 1).
+// ---------------------------------------------------------------------------------------------
+#define FERRIS_GATED_SILU 0
+#define FERRIS_GATED_GELU_TANH 1
+#define FERRIS_GATED_CLAMPED_SWISH 2
+__device__ __forceinline__ float ferris_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float ferris_gated_act(float g, float u, int kind, float limit) {
+    if (kind == FERRIS_GATED_GELU_TANH) return ferris_gelu_tanh(g) * u;
+    if (kind == FERRIS_GATED_CLAMPED_SWISH) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+    }
+    return (g / (1.0f + expf(-g))) * u;
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

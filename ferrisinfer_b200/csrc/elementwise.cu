@@ -736,3 +736,90 @@ FERRIS_API int ferris_softcap(float* z, long long n, float cap, void* stream) {
                   z, n, cap);
     FERRIS_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The gated feed-forward's activation as a kernel of its own: out[t, j] = f(gate_up[t, j], gate_up[t, I + j]) with f one
+// of the kinds of ferris_gated_act; rows of gate_up ld apart.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_activation_kernel(const T* gate_up, int ld, T* __restrict__ out, int tokens, int inter, int kind,
+                                        float limit) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t n = (size_t)tokens * inter;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter, j = i % inter;
+        const float g = to_float(gate_up[t * ld + j]);
+        const float u = to_float(gate_up[t * ld + inter + j]);
+        out[i] = from_float<T>(ferris_gated_act(g, u, kind, limit));
+    }
+}
+
+FERRIS_API int ferris_gated_activation(const void* gate_up, int ld, void* out, int dtype, int tokens, int inter, int kind,
+                                       float limit, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (inter <= 0 || ld < 2 * inter) FERRIS_REFUSE("gated activation: intermediate=%d in rows of %d", inter, ld);
+    if (kind < 0 || kind > 2) FERRIS_REFUSE("gated activation: unknown kind %d", kind);
+    const size_t n = (size_t)tokens * inter;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(gated_activation_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, ld, (float*)out, tokens, inter, kind, limit);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(gated_activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)gate_up, ld, (bf16*)out, tokens, inter, kind, limit);
+    else
+        FERRIS_REFUSE("gated activation: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[t, j] = x[t, j] * a(gate[t, j]) * scale, a = sigmoid (kind 0) or SiLU (kind 1); rows ldx / ldg / ldo apart; out may
+// be x.  The gate of an attention's output: the heads side by side times a function of a projection of the layer's input.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_mul_kernel(const T* x, int ldx, const T* gate, int ldg, T* out, int ldo, int rows, int n, int kind,
+                                float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t total = (size_t)rows * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / n, j = i % n;
+        const float z = to_float(gate[t * ldg + j]);
+        const float sg = 1.0f / (1.0f + expf(-z));
+        out[t * ldo + j] = from_float<T>(to_float(x[t * ldx + j]) * (kind == 1 ? z * sg : sg) * scale);
+    }
+}
+
+FERRIS_API int ferris_gate_mul(const void* x, int ldx, const void* gate, int ldg, void* out, int ldo, int dtype, int rows,
+                               int n, int kind, float scale, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (n <= 0 || ldx < n || ldg < n || ldo < n) FERRIS_REFUSE("gate: %d columns in rows of %d, %d, %d", n, ldx, ldg, ldo);
+    if (kind != 0 && kind != 1) FERRIS_REFUSE("gate: unknown kind %d", kind);
+    const size_t total = (size_t)rows * n;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FERRIS_F32)
+        ferris_launch(gate_mul_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)x, ldx, (const float*)gate, ldg, (float*)out, ldo, rows, n, kind, scale);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(gate_mul_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)x, ldx, (const bf16*)gate, ldg, (bf16*)out, ldo, rows, n, kind, scale);
+    else
+        FERRIS_REFUSE("gate: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// logits <- logits * scale in place; fp32.
+__global__ void scale_kernel(float* x, long long n, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= scale;
+}
+
+FERRIS_API int ferris_scale(float* x, long long n, float scale, void* stream) {
+    if (n <= 0) return FERRIS_OK;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    ferris_launch(scale_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(threads), 0, (cudaStream_t)stream, x, n, scale);
+    FERRIS_LAUNCH_CHECK();
+}

@@ -9,6 +9,9 @@
 // or a gate) are one fp32 number per token and head, made by `recurrence_gates`; q and k come in `qk_heads` heads
 // shared by heads / qk_heads value heads each, and may carry one fp32 factor per (token, qk head) each (unit norms:
 // the factor is 1 / |x|, formed in fp32 by the gates kernel, so that the vectors themselves are read once as stored).
+// The plain form also takes a decay per ROW of the state (per key channel) that changes with every token, given as
+// fp32 numbers z per (token, head, row): the row's decay is sigmoid(z)^power = exp(-softplus(-z) * power), formed
+// in fp32 where the rows are staged; the decay per head is then left out (gated linear attention).
 //
 // The columns of S do not depend on one another.  4, 8, 16 or 32 lanes (by the head's size) share a column, each
 // holding eight rows of it in registers (rows sub, sub + lanes, ...), and a block of 128 threads owns 32, 16, 8 or 4
@@ -75,19 +78,21 @@ __global__ void __launch_bounds__(128) recurrence_gates_kernel(const T* proj, in
 
 // LANES lanes share a column, GR_KPL rows each: dim <= GR_KPL * LANES.  AHEAD: the next tokens are requested into registers
 // while the present ones are worked on (portions of prompts); without it a stage goes straight to shared memory.
-template <typename T, int LANES, bool DELTA, bool AHEAD>
+template <typename T, int LANES, bool DELTA, bool AHEAD, bool ROWDECAY = false>
 __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     const T* q, int ldq, const T* k, int ldk, const T* v, int ldv, const float* decay, const float* beta,
     const float* qscale, const float* kscale, const float* __restrict__ skip, float* __restrict__ out, int ldo,
     float* state, const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot, int heads, int qk_heads,
-    int dim, int vdim, int write_state) {
+    int dim, int vdim, int write_state, const float* row_z, int ldz, float row_power, float q_mul) {
     constexpr int COLS = GR_THREADS / LANES;  // columns of a block
+    constexpr int STAGE = (ROWDECAY && LANES == 32) ? GR_STAGE / 2 : GR_STAGE;  // three staged vectors of 256 rows: fewer tokens
     constexpr int ROWS = GR_KPL * LANES;      // rows of the state that the lanes of a column hold
-    constexpr int VP = (GR_STAGE * COLS + GR_THREADS - 1) / GR_THREADS;  // values a thread brings per stage
-    __shared__ float qs[GR_STAGE][ROWS];
-    __shared__ float ks[GR_STAGE][ROWS];
-    __shared__ float vs[GR_STAGE][COLS];
-    __shared__ float gs[GR_STAGE], bs[GR_STAGE], fqs[GR_STAGE], fks[GR_STAGE];
+    constexpr int VP = (STAGE * COLS + GR_THREADS - 1) / GR_THREADS;  // values a thread brings per stage
+    __shared__ float qs[STAGE][ROWS];
+    __shared__ float ks[STAGE][ROWS];
+    __shared__ float vs[STAGE][COLS];
+    __shared__ float gs[STAGE], bs[STAGE], fqs[STAGE], fks[STAGE];
+    __shared__ float as[ROWDECAY ? STAGE : 1][ROWDECAY ? ROWS : 1];  // the rows' decays of the staged tokens
     pdl_wait();
     pdl_launch_dependents();
     const int seq = blockIdx.x, head = blockIdx.y;
@@ -106,16 +111,20 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
         s[i] = (active && kk < dim) ? S[kk] : 0.0f;
     }
     // rows of the staged vectors beyond the head's size stay zero
-    for (int i = tid; i < GR_STAGE * ROWS; i += GR_THREADS) (&qs[0][0])[i] = 0.0f, (&ks[0][0])[i] = 0.0f;
+    for (int i = tid; i < STAGE * ROWS; i += GR_THREADS) {
+        (&qs[0][0])[i] = 0.0f, (&ks[0][0])[i] = 0.0f;
+        if (ROWDECAY) (&as[0][0])[i] = 0.0f;
+    }
     const float d_skip = skip ? skip[head] : 0.0f;
     // A stage's q, k, v and per-token numbers are requested into registers while the stage before it is worked on
     // (the requests of a stage are all in flight together), and go to shared memory when that one is done.
     // (they stay as they were loaded until then: an instruction that touched one would wait for its load)
-    T pq[GR_STAGE][2], pk[GR_STAGE][2], pv[VP];
+    T pq[STAGE][2], pk[STAGE][2], pv[VP];
+    float pz[ROWDECAY ? STAGE : 1][2];
     float pg = 0.0f, pb = 0.0f, pfq = 1.0f, pfk = 1.0f;
     auto request = [&](int t0) {
 #pragma unroll
-        for (int r = 0; r < GR_STAGE; ++r) {
+        for (int r = 0; r < STAGE; ++r) {
             if (t0 + r >= row1) break;  // a single token's block asks for one row
             const size_t row = (size_t)(t0 + r);
 #pragma unroll
@@ -124,6 +133,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 if (c < dim) {
                     pq[r][j] = q[row * ldq + (size_t)qh * dim + c];
                     pk[r][j] = k[row * ldk + (size_t)qh * dim + c];
+                    if (ROWDECAY) pz[r][j] = row_z[row * ldz + (size_t)head * dim + c];
                 }
             }
         }
@@ -132,19 +142,19 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
             const int e = tid + j * GR_THREADS, r = e / COLS, c = e % COLS;
             const int cc = blockIdx.z * COLS + c;
             pv[j] = from_float<T>(0.0f);
-            if (e < GR_STAGE * COLS && t0 + r < row1 && cc < vdim) pv[j] = v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc];
+            if (e < STAGE * COLS && t0 + r < row1 && cc < vdim) pv[j] = v[(size_t)(t0 + r) * ldv + (size_t)head * vdim + cc];
         }
-        if (tid < GR_STAGE && t0 + tid < row1) {
+        if (tid < STAGE && t0 + tid < row1) {
             const size_t row = (size_t)(t0 + tid);
-            pg = decay[row * heads + head];
-            pb = beta[row * heads + head];
+            pg = decay ? decay[row * heads + head] : 1.0f;
+            pb = beta ? beta[row * heads + head] : 1.0f;
             pfq = qscale ? qscale[row * qk_heads + qh] : 1.0f;
             pfk = kscale ? kscale[row * qk_heads + qh] : 1.0f;
         }
     };
     if (AHEAD) request(row0);
-    for (int t0 = row0; t0 < row1; t0 += GR_STAGE) {
-        const int n = row1 - t0 < GR_STAGE ? row1 - t0 : GR_STAGE;
+    for (int t0 = row0; t0 < row1; t0 += STAGE) {
+        const int n = row1 - t0 < STAGE ? row1 - t0 : STAGE;
         __syncthreads();  // the tokens before are done with (and the zeroing above has landed)
         if (!AHEAD) {  // a few tokens a request (a step of single tokens): straight into shared memory
             for (int i = tid; i < n * dim; i += GR_THREADS) {
@@ -152,6 +162,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 const size_t row = (size_t)(t0 + r);
                 qs[r][c] = to_float(q[row * ldq + (size_t)qh * dim + c]);
                 ks[r][c] = to_float(k[row * ldk + (size_t)qh * dim + c]);
+                if (ROWDECAY) as[r][c] = expf(-softplus_g(-row_z[row * ldz + (size_t)head * dim + c]) * row_power);
             }
             for (int i = tid; i < n * COLS; i += GR_THREADS) {
                 const int r = i / COLS, c = i - r * COLS;
@@ -160,19 +171,22 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
             }
             if (tid < n) {
                 const size_t row = (size_t)(t0 + tid);
-                gs[tid] = decay[row * heads + head];
-                bs[tid] = beta[row * heads + head];
+                gs[tid] = decay ? decay[row * heads + head] : 1.0f;
+                bs[tid] = beta ? beta[row * heads + head] : 1.0f;
                 fqs[tid] = qscale ? qscale[row * qk_heads + qh] : 1.0f;
                 fks[tid] = kscale ? kscale[row * qk_heads + qh] : 1.0f;
             }
         } else {
 #pragma unroll
-        for (int r = 0; r < GR_STAGE; ++r) {
+        for (int r = 0; r < STAGE; ++r) {
             if (r >= n) break;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int c = tid + j * GR_THREADS;
-                if (c < dim) qs[r][c] = to_float(pq[r][j]), ks[r][c] = to_float(pk[r][j]);
+                if (c < dim) {
+                    qs[r][c] = to_float(pq[r][j]), ks[r][c] = to_float(pk[r][j]);
+                    if (ROWDECAY) as[r][c] = expf(-softplus_g(-pz[r][j]) * row_power);
+                }
             }
         }
 #pragma unroll
@@ -180,10 +194,10 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
             const int e = tid + j * GR_THREADS;
             if (e < n * COLS) (&vs[0][0])[e] = to_float(pv[j]);
         }
-        if (tid < GR_STAGE) gs[tid] = pg, bs[tid] = pb, fqs[tid] = pfq, fks[tid] = pfk;
+        if (tid < STAGE) gs[tid] = pg, bs[tid] = pb, fqs[tid] = pfq, fks[tid] = pfk;
         }
         __syncthreads();
-        if (AHEAD && t0 + GR_STAGE < row1) request(t0 + GR_STAGE);
+        if (AHEAD && t0 + STAGE < row1) request(t0 + STAGE);
         for (int r = 0; r < n; ++r) {
             const float g = gs[r], b = bs[r], vv = vs[r][cl], fq = fqs[r], fk = fks[r];
             float kr[GR_KPL], qr[GR_KPL];
@@ -211,14 +225,16 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 uk = (b * vv) * fk;
 #pragma unroll
                 for (int i = 0; i < GR_KPL; i += 2) {
-                    s[i] = fmaf(g, s[i], kr[i] * uk), s[i + 1] = fmaf(g, s[i + 1], kr[i + 1] * uk);
+                    const float g0 = ROWDECAY ? as[r][sub + LANES * i] : g;
+                    const float g1 = ROWDECAY ? as[r][sub + LANES * (i + 1)] : g;
+                    s[i] = fmaf(g0, s[i], kr[i] * uk), s[i + 1] = fmaf(g1, s[i + 1], kr[i + 1] * uk);
                     od0 = fmaf(s[i], qr[i], od0), od1 = fmaf(s[i + 1], qr[i + 1], od1);
                 }
             }
             float od = od0 + od1;
 #pragma unroll
             for (int o = 1; o < LANES; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
-            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, fq * od);
+            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, (fq * q_mul) * od);
         }
     }
     if (write_state && active) {
@@ -307,17 +323,18 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, i
     }
 }
 
-template <typename T, bool DELTA, bool AHEAD>
+template <typename T, bool DELTA, bool AHEAD, bool ROWDECAY = false>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* decay,
                       const float* beta, const float* qscale, const float* kscale, const float* skip, float* out, int ldo,
                       float* state, const int* seq_q_start, const int* seq_state_slot, int seqs, int heads, int qk_heads,
-                      int dim, int vdim, int write_state, cudaStream_t s) {
+                      int dim, int vdim, int write_state, cudaStream_t s, const float* row_z = nullptr, int ldz = 0,
+                      float row_power = 1.0f, float q_mul = 1.0f) {
     const dim3 block(GR_THREADS);
 #define FERRIS_GR_LAUNCH(LANES)                                                                                         \
-    ferris_launch(gated_recurrence_kernel<T, LANES, DELTA, AHEAD>,                                                             \
+    ferris_launch(gated_recurrence_kernel<T, LANES, DELTA, AHEAD, ROWDECAY>,                                          \
                   dim3(seqs, heads, (vdim + GR_THREADS / LANES - 1) / (GR_THREADS / LANES)), block, 0, s, (const T*)q, \
                   ldq, (const T*)k, ldk, (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state,          \
-                  seq_q_start, seq_state_slot, heads, qk_heads, dim, vdim, write_state)
+                  seq_q_start, seq_state_slot, heads, qk_heads, dim, vdim, write_state, row_z, ldz, row_power, q_mul)
     if (dim <= 32)
         FERRIS_GR_LAUNCH(4);
     else if (dim <= 64)
@@ -382,6 +399,28 @@ FERRIS_API int ferris_gated_recurrence(const void* q, int ldq, const void* k, in
     if (delta_rule) { if (ahead) FERRIS_GR_GO(bf16, true, true); else FERRIS_GR_GO(bf16, true, false); }
     if (ahead) FERRIS_GR_GO(bf16, false, true); else FERRIS_GR_GO(bf16, false, false);
 #undef FERRIS_GR_GO
+}
+
+// The plain form with a decay per row of the state: row_z fp32 [tokens, heads x dim], rows ldz apart; the decay of
+// row r of head h at token t is sigmoid(row_z[t, h, r])^row_power.  q and k come in `heads` heads; out = q_mul S^T q.
+FERRIS_API int ferris_row_decay_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int dtype,
+                                           const float* row_z, int ldz, float row_power, float q_mul, float* out, int ldo,
+                                           float* state, const int* seq_q_start, const int* seq_state_slot, int seqs,
+                                           int heads, int dim, int vdim, int write_state, int longest, void* stream) {
+    if (seqs <= 0) return FERRIS_OK;
+    if (heads <= 0 || !row_z) FERRIS_REFUSE("row-decay recurrence: %d heads, or no decays", heads);
+    if (dim <= 0 || dim > GR_MAX_DIM || vdim <= 0) FERRIS_REFUSE("row-decay recurrence: heads of %d x %d (at most %d rows)", dim, vdim, GR_MAX_DIM);
+    if (heads > 65535 || (vdim + 3) / 4 > 65535) FERRIS_REFUSE("row-decay recurrence: too many heads or columns for one launch");
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("row-decay recurrence: unknown dtype %d", dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool ahead = longest > GR_STAGE;
+#define FERRIS_RD_GO(T, A)                                                                                                   \
+    return launch_recurrence<T, false, A, true>(q, ldq, k, ldk, v, ldv, nullptr, nullptr, nullptr, nullptr, nullptr, out, ldo, \
+                                                state, seq_q_start, seq_state_slot, seqs, heads, heads, dim, vdim, write_state, \
+                                                s, row_z, ldz, row_power, q_mul)
+    if (dtype == FERRIS_F32) { if (ahead) FERRIS_RD_GO(float, true); else FERRIS_RD_GO(float, false); }
+    if (ahead) FERRIS_RD_GO(bf16, true); else FERRIS_RD_GO(bf16, false);
+#undef FERRIS_RD_GO
 }
 
 // o: fp32 [rows, n]; gate (may be null), out: the activations' type; w: fp32 [wlen], wlen dividing n.

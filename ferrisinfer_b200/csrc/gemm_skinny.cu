@@ -76,7 +76,10 @@ __device__ __forceinline__ float sk_silu_mul(float g, float u) { return u * (g *
 // others are the code they were).
 template <bool ACT>
 __device__ __forceinline__ void sk_write(const SkParams& p, int t, int n, float a, float b, float bias_v, float old) {
-    if (ACT) {
+    if (ACT && p.mode == SK_SWIGLU_BF16) {
+        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] =
+            __float2bfloat16_rn(ferris_gated_act(a, b, p.act.kind - FERRIS_EPILOGUE_GATED, p.act.a));
+    } else if (ACT) {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(ferris_epilogue_act(a + bias_v, p.act));
     } else if (p.mode == SK_STORE_BF16) {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + bias_v);
@@ -539,7 +542,8 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (mode < 0 || mode > 3) FERRIS_REFUSE("skinny gemm: unknown mode %d", mode);
     const FerrisEpilogueAct act = ferris_take_epilogue_act();
-    if (act.kind && mode != SK_STORE_BF16) FERRIS_REFUSE("skinny gemm: an activation goes with the bf16 store, not mode %d", mode);
+    if (act.kind && (act.kind >= FERRIS_EPILOGUE_GATED ? mode != SK_SWIGLU_BF16 : mode != SK_STORE_BF16))
+        FERRIS_REFUSE("skinny gemm: activation %d does not go with mode %d", act.kind, mode);
     const int accs = mode == SK_SWIGLU_BF16 ? 2 : 1;
     SkPlan plan;
     if (!sk_plan(T, N, K, accs, norm_h == nullptr, &plan))
@@ -596,6 +600,8 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
     p.status = ferris_status_ptr();
     p.act = act;
     cudaStream_t s = (cudaStream_t)stream;
+    if (accs == 2 && act.kind)
+        return T > 8 ? sk_launch<2, 2, true>(mw, mx, p, plan.ctas, plan.smem, s) : sk_launch<2, 1, true>(mw, mx, p, plan.ctas, plan.smem, s);
     if (accs == 2)
         return T > 8 ? sk_launch<2, 2>(mw, mx, p, plan.ctas, plan.smem, s) : sk_launch<2, 1>(mw, mx, p, plan.ctas, plan.smem, s);
     if (act.kind)

@@ -814,8 +814,13 @@ __device__ __forceinline__ void pt_epilogue_tile(const PTParams& p, const CUtens
             for (int c = 0; c < 32; c += 2) {
                 float v0, v1;
                 if (MODE == SWIGLU_BF16) {
-                    v0 = silu_mul(__uint_as_float(ra[c]), __uint_as_float(rb[c]));
-                    v1 = silu_mul(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]));
+                    if (p.act.kind) {  // another gated activation than SiLU
+                        v0 = ferris_gated_act(__uint_as_float(ra[c]), __uint_as_float(rb[c]), p.act.kind - FERRIS_EPILOGUE_GATED, p.act.a);
+                        v1 = ferris_gated_act(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]), p.act.kind - FERRIS_EPILOGUE_GATED, p.act.a);
+                    } else {
+                        v0 = silu_mul(__uint_as_float(ra[c]), __uint_as_float(rb[c]));
+                        v1 = silu_mul(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]));
+                    }
                 } else {
                     v0 = __uint_as_float(ra[c]) + ((p.bias && n + c < p.N) ? __ldg(p.bias + n + c) : 0.0f);
                     v1 = __uint_as_float(ra[c + 1]) + ((p.bias && n + c + 1 < p.N) ? __ldg(p.bias + n + c + 1) : 0.0f);
@@ -1485,6 +1490,10 @@ struct TokenSource {
 FERRIS_API int ferris_gemm_tcgen05_fuses_activation(int T, int N, int K, int ldo, const void* out) {
     return token_major_pays(0 /* STORE_BF16 */, T, N, K) && ((size_t)ldo * 2) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
 }
+// The same question for a product of two accumulators and its gated activation.
+FERRIS_API int ferris_gemm_tcgen05_fuses_gated_activation(int T, int N, int K, int ldo, const void* out) {
+    return token_major_pays(3 /* SWIGLU_BF16 */, T, N, K) && ((size_t)ldo * 2) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+}
 
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
@@ -1625,7 +1634,9 @@ FERRIS_API int ferris_gemm_grouped_tcgen05(const void* x, const void* w, void* o
         FERRIS_REFUSE("grouped gemm: %d outputs (+%d) from %d rows an expert", N, up_row_offset, expert_rows);
     const int elt = mode == STORE_F32 ? 4 : 2;
     if (ldo < N || ((size_t)ldo * elt) % 16 || ((uintptr_t)out & 15)) FERRIS_REFUSE("grouped gemm: output rows must start on 16 bytes");
-    g_launch_act = FerrisEpilogueAct{0, 0.0f, 0.0f};
+    g_launch_act = ferris_take_epilogue_act();
+    if (g_launch_act.kind && (g_launch_act.kind >= FERRIS_EPILOGUE_GATED) != (mode == SWIGLU_BF16))
+        FERRIS_REFUSE("grouped gemm: activation %d does not go with mode %d", g_launch_act.kind, mode);
     return run_tokens_m(x, w, nullptr, out, mode, rows, N, K, ldx, ldw, ldo, experts * expert_rows, up_row_offset, nullptr,
                         (cudaStream_t)stream, tile_expert, expert_rows);
 }
@@ -1640,8 +1651,8 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FERRIS_REFUSE("tensor-core gemm: operands must be 16-byte aligned");
     if (mode < 0 || mode > 3) FERRIS_REFUSE("tensor-core gemm: unknown mode %d", mode);
     g_launch_act = ferris_take_epilogue_act();
-    if (g_launch_act.kind && mode != STORE_BF16)
-        FERRIS_REFUSE("tensor-core gemm: an activation goes with the bf16 store, not mode %d", mode);
+    if (g_launch_act.kind && (g_launch_act.kind >= FERRIS_EPILOGUE_GATED ? mode != SWIGLU_BF16 : mode != STORE_BF16))
+        FERRIS_REFUSE("tensor-core gemm: activation %d does not go with mode %d", g_launch_act.kind, mode);
     if (mode == SWIGLU_BF16 && (bias || up_row_offset + N > rows_w)) FERRIS_REFUSE("tensor-core gemm: bad SwiGLU operands");
     if (mode != SWIGLU_BF16 && N > rows_w) FERRIS_REFUSE("tensor-core gemm: %d outputs from %d weight rows", N, rows_w);
     if (ldo < N) FERRIS_REFUSE("tensor-core gemm: output row stride %d < %d", ldo, N);

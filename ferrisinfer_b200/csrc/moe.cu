@@ -5,6 +5,15 @@
 //   expert e  a_e = silu(Wg_e y) * (Wu_e y);  o_e = Wd_e a_e
 //   result    h (+)= sum over the chosen experts, in the order in which they were chosen, of weight_e o_e
 //
+// A second kind of router (`scored`): s = softmax(z) over ALL router outputs; the choice is made by c = s + correction
+// (a learned number per output), the outputs stand in `groups` equal groups of neighbours of which only the `keep`
+// with the largest c in them take part (the others count as minus infinity), the `top` largest c are chosen (the
+// lowest index among equals) and their weights are s / (sum of the chosen s + 1e-20).  Router outputs beyond the
+// experts with weights are identity experts, whose result is the token's row itself: the router hands them on as one
+// index past the last expert, which every expert kernel skips, and leaves the sum of their weights per token, which
+// the adding passes multiply the token's row by.  The experts' gated activation is one of the kinds of
+// ferris_gated_act.
+//
 // The experts' matrices lie stacked: gate and up as [experts, ff, width] each, down as [experts, width, ff].
 //
 // Three ways through the experts.  Token-major (a single choice; the 32-bit path of long steps): a block per (token, chosen expert) and
@@ -240,14 +249,16 @@ template <typename T, bool BLOCK>
 __global__ void __launch_bounds__(128) moe_router_kernel(const T* x, int ldx, const T* __restrict__ w,
                                                          const float* __restrict__ bias, int* __restrict__ ids,
                                                          float* __restrict__ weights, int tokens, int width, int experts,
-                                                         int top) {
-    extern __shared__ __align__(16) float smem[];  // per warp (per block): the token's row (width) and its logits (experts)
+                                                         int top, int scored, const float* __restrict__ correction,
+                                                         int groups, int keep, int with_weights,
+                                                         float* __restrict__ identity_w) {
+    extern __shared__ __align__(16) float smem[];  // per warp (per block): the token's row (width), its logits (experts), and for the scored kind the choice scores (experts) and the groups' (experts at most)
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = BLOCK ? blockIdx.x : blockIdx.x * 4 + warp;
     if (t >= tokens) return;
-    float* xs = smem + (BLOCK ? 0 : (size_t)warp * ((width + experts + 3) & ~3));  // every warp's row starts on 16 bytes
+    float* xs = smem + (BLOCK ? 0 : (size_t)warp * ((width + 3 * experts + 3) & ~3));  // every warp's row starts on 16 bytes
     float* z = xs + width;
     const T* xr = x + (size_t)t * ldx;
     if (BLOCK) {
@@ -267,6 +278,79 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T* x, int ldx, co
         if (warp) return;
     } else {
         __syncwarp();
+    }
+    if (scored) {
+        float* c = z + experts;
+        float* gsc = c + experts;
+        float mx = -INFINITY;
+        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float total = 0.0f;
+        for (int e = lane; e < experts; e += 32) total += expf(z[e] - mx);
+        total = warp_sum(total);
+        for (int e = lane; e < experts; e += 32) {
+            const float p = expf(z[e] - mx) / total;
+            z[e] = p, c[e] = p + (correction ? correction[e] : 0.0f);
+        }
+        __syncwarp();
+        const int size = experts / groups;
+        if (keep < groups) {
+            for (int g = lane; g < groups; g += 32) {
+                float best = -INFINITY;
+                for (int j = 0; j < size; ++j) best = fmaxf(best, c[g * size + j]);
+                gsc[g] = best;
+            }
+            __syncwarp();
+            for (int round = 0; round < keep; ++round) {  // the best group that is left; +inf marks a group that stays
+                float best = -INFINITY;
+                int at = groups;
+                for (int g = lane; g < groups; g += 32) {
+                    const float v = gsc[g];
+                    if (v != INFINITY && (v > best || at == groups)) best = v, at = g;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (oa < groups && (at == groups || ob > best || (ob == best && oa < at))) best = ob, at = oa;
+                }
+                if (lane == 0 && at < groups) gsc[at] = INFINITY;
+                __syncwarp();
+            }
+            for (int e = lane; e < experts; e += 32)
+                if (gsc[e / size] != INFINITY) c[e] = -INFINITY;
+            __syncwarp();
+        }
+        float chosen_p = 0.0f;
+        int chosen = 0;
+        for (int s = 0; s < top; ++s) {
+            float best = -INFINITY;
+            int at = experts;
+            for (int e = lane; e < experts; e += 32) {
+                const float v = c[e];
+                if (v > best) best = v, at = e;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) best = ob, at = oa;
+            }
+            if (at >= experts) at = s < experts ? s : 0;  // only where scores are not numbers
+            if (lane == (s & 31) && s < 32) chosen = at, chosen_p = z[at];
+            if (lane == 0) c[at] = -INFINITY;
+            __syncwarp();
+        }
+        const float denom = warp_sum(lane < top ? chosen_p : 0.0f) + 1e-20f;
+        const float wgt = chosen_p / denom;
+        const bool identity = lane < top && chosen >= with_weights;
+        const float idw = warp_sum(identity ? wgt : 0.0f);
+        if (lane < top) {
+            ids[(size_t)t * top + lane] = identity ? with_weights : chosen;
+            weights[(size_t)t * top + lane] = wgt;
+        }
+        if (identity_w && lane == 0) identity_w[t] = idw;
+        return;
     }
     float chosen_z = 0.0f, first_z = 0.0f, sum = 0.0f;  // lane s keeps the s-th choice
     int chosen = 0;
@@ -301,12 +385,14 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T* x, int ldx, co
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, const T* __restrict__ gate,
                                                           const T* __restrict__ up, size_t expert_stride, const int* ids,
-                                                          T* __restrict__ act, int width, int ff, int top, int slab) {
+                                                          T* __restrict__ act, int width, int ff, int top, int slab,
+                                                          int experts, int act_kind, float act_limit) {
     extern __shared__ __align__(16) float xs[];  // the token's row
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pair = blockIdx.x, t = pair / top, e = ids[pair];
+    if (e >= experts) return;  // an identity expert: nothing to form
     const T* xr = x + (size_t)t * ldx;
     stage_row(xs, xr, width, threadIdx.x, blockDim.x);
     __syncthreads();
@@ -322,14 +408,14 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, c
             float d[4];
             dot_rows<4>(rows, xs, width, lane, vec, d);
             if (lane == 0) {
-                act[(size_t)pair * ff + j] = from_float<T>((d[0] / (1.0f + expf(-d[0]))) * d[1]);
-                act[(size_t)pair * ff + j + 4] = from_float<T>((d[2] / (1.0f + expf(-d[2]))) * d[3]);
+                act[(size_t)pair * ff + j] = from_float<T>(ferris_gated_act(d[0], d[1], act_kind, act_limit));
+                act[(size_t)pair * ff + j + 4] = from_float<T>(ferris_gated_act(d[2], d[3], act_kind, act_limit));
             }
         } else {
             const T* const rows[2] = {g + (size_t)j * width, u + (size_t)j * width};
             float d[2];
             dot_rows<2>(rows, xs, width, lane, vec, d);
-            if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>((d[0] / (1.0f + expf(-d[0]))) * d[1]);
+            if (lane == 0) act[(size_t)pair * ff + j] = from_float<T>(ferris_gated_act(d[0], d[1], act_kind, act_limit));
         }
     }
 }
@@ -338,7 +424,8 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* x, int ldx, c
 template <typename T>
 __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __restrict__ down, const int* ids,
                                                        const float* weights, float* h, int ldh, int width, int ff, int top,
-                                                       int slab, int accumulate) {
+                                                       int slab, int accumulate, int experts, const T* x, int ldx,
+                                                       const float* identity_w) {
     extern __shared__ __align__(16) float as[];  // the token's activations: top x ff
     __shared__ int es[MOE_MAX_TOP];
     __shared__ float ws[MOE_MAX_TOP];
@@ -347,9 +434,12 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x;
     const T* ar = act + (size_t)t * top * ff;
-    stage_row(as, ar, top * ff, threadIdx.x, blockDim.x);
     if (threadIdx.x < top) es[threadIdx.x] = ids[(size_t)t * top + threadIdx.x], ws[threadIdx.x] = weights[(size_t)t * top + threadIdx.x];
     __syncthreads();
+    for (int s = 0; s < top; ++s)  // the rows of identity experts were never written
+        if (es[s] < experts) stage_row(as + (size_t)s * ff, ar + (size_t)s * ff, ff, threadIdx.x, blockDim.x);
+    __syncthreads();
+    const float idw = identity_w ? identity_w[t] : 0.0f;
     const bool vec = rows_vectorise(down, ff) && (ff * sizeof(float)) % 16 == 0;
     const int c0 = blockIdx.y * slab, c1 = min(width, c0 + slab);
     // a warp takes columns c, c + 4, c + 8 and c + 12 at a time: four weight rows in flight for one read of the activations
@@ -357,6 +447,7 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
         float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const int n = min(4, (c1 - c + 3) / 4);
         for (int s = 0; s < top; ++s) {
+            if (es[s] >= experts) continue;
             const T* first = down + ((size_t)es[s] * width + c) * ff;
             const float* a = as + (size_t)s * ff;
             if (n == 4) {
@@ -372,6 +463,7 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const T* act, const T* __
         if (lane == 0) {
             for (int r = 0; r < n; ++r) {
                 float* dst = h + (size_t)t * ldh + c + 4 * r;
+                if (identity_w) sum[r] = fmaf(idw, to_float(x[(size_t)t * ldx + c + 4 * r]), sum[r]);
                 *dst = accumulate ? *dst + sum[r] : sum[r];
             }
         }
@@ -408,7 +500,7 @@ __device__ __forceinline__ int pairs_of_expert(const int* ids, int pairs, int e,
 template <typename T, int M>
 __device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float* xs, int width, int ff, int j0, int j1,
                                              const int* pair, T* __restrict__ act, int lane, int warp, bool vec,
-                                             uint4* ring) {
+                                             uint4* ring, int act_kind, float act_limit) {
     for (int j = j0 + warp; j < j1; j += 2 * FEW_WARPS) {
         if (j + FEW_WARPS < j1) {
             const T* const rows[4] = {g + (size_t)j * width, u + (size_t)j * width, g + (size_t)(j + FEW_WARPS) * width,
@@ -418,8 +510,8 @@ __device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float
             if (lane == 0) {
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
-                    act[(size_t)pair[m] * ff + j] = from_float<T>((d[0][m] / (1.0f + expf(-d[0][m]))) * d[1][m]);
-                    act[(size_t)pair[m] * ff + j + FEW_WARPS] = from_float<T>((d[2][m] / (1.0f + expf(-d[2][m]))) * d[3][m]);
+                    act[(size_t)pair[m] * ff + j] = from_float<T>(ferris_gated_act(d[0][m], d[1][m], act_kind, act_limit));
+                    act[(size_t)pair[m] * ff + j + FEW_WARPS] = from_float<T>(ferris_gated_act(d[2][m], d[3][m], act_kind, act_limit));
                 }
             }
         } else {
@@ -429,7 +521,7 @@ __device__ __forceinline__ void gate_up_rows(const T* g, const T* u, const float
             if (lane == 0) {
 #pragma unroll
                 for (int m = 0; m < M; ++m)
-                    act[(size_t)pair[m] * ff + j] = from_float<T>((d[0][m] / (1.0f + expf(-d[0][m]))) * d[1][m]);
+                    act[(size_t)pair[m] * ff + j] = from_float<T>(ferris_gated_act(d[0][m], d[1][m], act_kind, act_limit));
             }
         }
     }
@@ -439,7 +531,7 @@ template <typename T>
 __global__ void __launch_bounds__(32 * FEW_WARPS) moe_gate_up_few_kernel(const T* x, int ldx, const T* __restrict__ gate,
                                                               const T* __restrict__ up, size_t expert_stride, const int* ids,
                                                               T* __restrict__ act, int width, int ff, int pairs, int top,
-                                                              int slab) {
+                                                              int slab, int act_kind, float act_limit) {
     extern __shared__ __align__(16) float dyn[];  // every warp's slots for weights in flight, then MOE_FEW_ROWS token rows
     __shared__ int list[MOE_FEW_MAX_PAIRS];
     __shared__ int count;
@@ -463,10 +555,10 @@ __global__ void __launch_bounds__(32 * FEW_WARPS) moe_gate_up_few_kernel(const T
         __syncthreads();
         const int* pair = list + first;
         switch (m) {
-            case 1: gate_up_rows<T, 1>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
-            case 2: gate_up_rows<T, 2>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
-            case 3: gate_up_rows<T, 3>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
-            default: gate_up_rows<T, 4>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring); break;
+            case 1: gate_up_rows<T, 1>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring, act_kind, act_limit); break;
+            case 2: gate_up_rows<T, 2>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring, act_kind, act_limit); break;
+            case 3: gate_up_rows<T, 3>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring, act_kind, act_limit); break;
+            default: gate_up_rows<T, 4>(g, u, xs, width, ff, j0, j1, pair, act, lane, warp, vec, ring, act_kind, act_limit); break;
         }
     }
 }
@@ -536,7 +628,7 @@ __global__ void __launch_bounds__(32 * FEW_WARPS) moe_down_few_kernel(const T* a
 // only fills a tile up; tile_expert[tile] = the expert of the tile's rows, or -1 beyond the last row.
 constexpr int MOE_TILE = 128;
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* ids, int* pos, int* row_token, int* tile_expert,
-                                                        int pairs, int top, int experts, int max_rows) {
+                                                        int pairs, int top, int experts, int max_rows, int with_weights) {
     __shared__ int count[MOE_MAX_EXPERTS];
     __shared__ int first[MOE_MAX_EXPERTS + 1];
     pdl_wait();
@@ -569,7 +661,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* ids, int* pos
                 const int mid = (lo + hi + 1) >> 1;
                 if (first[mid] <= row) lo = mid; else hi = mid - 1;
             }
-            e = lo;
+            e = lo < with_weights ? lo : -1;  // the rows of identity experts meet no weights
         }
         tile_expert[tile] = e;
     }
@@ -590,9 +682,11 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* x, int ldx
 
 // h[t] (+)= sum_s weights[t, s] * y[pos[t, s]] (without pos: y[t x top + s]), in the order of the choices; four columns
 // a thread.
+template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ldy, const int* pos, const float* weights,
                                                           float* h, int ldh, int tokens, int width4, int top,
-                                                          int accumulate) {
+                                                          int accumulate, const int* ids, int experts, const T* x, int ldx,
+                                                          const float* identity_w) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t n = (size_t)tokens * width4;
@@ -602,10 +696,17 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ld
         float4 acc = accumulate ? *dst : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         for (int s = 0; s < top; ++s) {
+            if (ids && ids[(size_t)t * top + s] >= experts) continue;  // an identity expert: its row was never written
             const float w = weights[(size_t)t * top + s];
             const size_t row = pos ? (size_t)pos[(size_t)t * top + s] : (size_t)t * top + s;
             const float4 v = reinterpret_cast<const float4*>(y + row * ldy)[i];
             sum.x = fmaf(w, v.x, sum.x), sum.y = fmaf(w, v.y, sum.y), sum.z = fmaf(w, v.z, sum.z), sum.w = fmaf(w, v.w, sum.w);
+        }
+        if (identity_w) {
+            const float w = identity_w[t];
+            const T* xr = x + (size_t)t * ldx + 4 * i;
+            sum.x = fmaf(w, to_float(xr[0]), sum.x), sum.y = fmaf(w, to_float(xr[1]), sum.y);
+            sum.z = fmaf(w, to_float(xr[2]), sum.z), sum.w = fmaf(w, to_float(xr[3]), sum.w);
         }
         acc.x += sum.x, acc.y += sum.y, acc.z += sum.z, acc.w += sum.w;
         *dst = acc;
@@ -614,6 +715,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y, int ld
 
 }  // namespace
 
+extern "C" void ferris_gemm_set_gated_activation(int kind, float limit);
 extern "C" int ferris_gemm_grouped_tcgen05(const void* x, const void* w, void* out, int mode, int rows, int N, int K,
                                            int ldx, int ldw, int ldo, int experts, int expert_rows, int up_row_offset,
                                            const int* tile_expert, void* stream);
@@ -629,43 +731,65 @@ FERRIS_API int ferris_moe_sorted_rows(int tokens, int top, int experts) {
 // expert's gate rows, then its up rows); down bf16 [experts, width, ff]; ids, weights [tokens, top]; h fp32.
 // Scratch, all sized for rows = ferris_moe_sorted_rows(...): pos int32 [tokens x top], row_token int32 [rows],
 // tile_expert int32 [rows / 128], xs bf16 [rows, width], act bf16 [rows, ff], y fp32 [rows, width].
+// identity_w (may be null): fp32 [tokens]; with it, ids may hold `experts` (an identity expert: the pair meets no weights)
+// and h also gets identity_w[t] x[t]; the scratch is then sized for experts + 1.  act_kind, act_limit: the gated
+// activation (ferris_gated_act).
 FERRIS_API int ferris_moe_experts_grouped(const void* x, int ldx, const void* gate_up, const void* down, const int* ids,
                                           const float* weights, float* h, int ldh, int tokens, int width, int ff, int top,
                                           int experts, int rows, int* pos, int* row_token, int* tile_expert, void* xs,
-                                          void* act, float* y, int accumulate, void* stream) {
+                                          void* act, float* y, int accumulate, int act_kind, float act_limit,
+                                          const float* identity_w, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
-    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts)
+    const int sorted = experts + (identity_w ? 1 : 0);  // the identity experts' pairs sort behind the last expert's
+    if (experts <= 0 || sorted > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP)
         FERRIS_REFUSE("experts: %d of %d experts", top, experts);
-    if (rows != ferris_moe_sorted_rows(tokens, top, experts)) FERRIS_REFUSE("experts: scratch for %d rows", rows);
+    if (rows != ferris_moe_sorted_rows(tokens, top, sorted)) FERRIS_REFUSE("experts: scratch for %d rows", rows);
     if (width % 8 || ff % 8 || ldx % 8 || ldh % 4 || (((uintptr_t)x | (uintptr_t)xs | (uintptr_t)y | (uintptr_t)h) & 15))
         FERRIS_REFUSE("experts: width %d, ff %d and the rows must be multiples of 8 elements and start on 16 bytes", width, ff);
     cudaStream_t s = (cudaStream_t)stream;
-    ferris_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, ids, pos, row_token, tile_expert, tokens * top, top, experts,
-                  rows);
+    ferris_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, s, ids, pos, row_token, tile_expert, tokens * top, top, sorted,
+                  rows, experts);
     const size_t n16 = (size_t)rows * (width / 8);
     const size_t want = (n16 + 255) / 256;
     ferris_launch(moe_gather_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, s, (const uint4*)x,
                   ldx / 8, (const int*)row_token, (uint4*)xs, rows, width / 8);
+    ferris_gemm_set_gated_activation(act_kind, act_limit);  // taken by the product launched next
     int rc = ferris_gemm_grouped_tcgen05(xs, gate_up, act, 3, rows, ff, width, width, width, ff, experts, 2 * ff, ff,
                                          tile_expert, stream);
+    ferris_gemm_set_gated_activation(0, 0.0f);
     if (rc != FERRIS_OK) return rc;
     rc = ferris_gemm_grouped_tcgen05(act, down, y, 1, rows, width, ff, ff, ff, width, experts, width, 0, tile_expert, stream);
     if (rc != FERRIS_OK) return rc;
     const size_t n4 = (size_t)tokens * (width / 4);
     const size_t want4 = (n4 + 255) / 256;
-    ferris_launch(moe_combine_kernel, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s, (const float*)y,
-                  width, (const int*)pos, weights, h, ldh, tokens, width / 4, top, accumulate);
+    ferris_launch(moe_combine_kernel<bf16>, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s, (const float*)y,
+                  width, (const int*)pos, weights, h, ldh, tokens, width / 4, top, accumulate,
+                  identity_w ? ids : (const int*)nullptr, experts, (const bf16*)x, ldx, identity_w);
     FERRIS_LAUNCH_CHECK();
 }
 
+// scored = 0: the `top` largest logits (+ bias), softmax over those.  scored = 1: see the head of this file; `bias` is
+// unused, `correction` fp32 [experts] (may be null), with_weights = the experts that have weights (the router outputs
+// from there on are identity experts, handed on as the index with_weights), identity_w fp32 [tokens] (the sum of a token's
+// identity weights; may be null when with_weights == experts).
 FERRIS_API int ferris_moe_router(const void* x, int ldx, int dtype, const void* w, const float* bias, int* ids,
-                                 float* weights, int tokens, int width, int experts, int top, void* stream) {
+                                 float* weights, int tokens, int width, int experts, int top, int scored,
+                                 const float* correction, int groups, int keep, int with_weights, float* identity_w,
+                                 void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || top > MOE_MAX_TOP || width <= 0)
         FERRIS_REFUSE("router: %d experts (at most %d), %d chosen (at most %d), width %d", experts, MOE_MAX_EXPERTS, top,
                       MOE_MAX_TOP, width);
+    if (scored) {
+        if (groups <= 0 || experts % groups || keep < 1 || keep > groups || top > keep * (experts / groups))
+            FERRIS_REFUSE("router: %d outputs in %d groups of which %d stay, %d chosen", experts, groups, keep, top);
+        if (with_weights < 0 || with_weights > experts || (with_weights < experts && !identity_w))
+            FERRIS_REFUSE("router: %d of %d outputs have weights", with_weights, experts);
+    } else {
+        with_weights = experts;
+    }
     const bool per_block = tokens <= 148 * 2;  // few tokens: a block each, so that more warps share the work
-    const size_t smem = (per_block ? 1 : 4) * (size_t)((width + experts + 3) & ~3) * sizeof(float);
+    const size_t smem = (per_block ? 1 : 4) * (size_t)((width + 3 * experts + 3) & ~3) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(per_block ? tokens : (tokens + 3) / 4), block(128);
     int rc;
@@ -673,7 +797,7 @@ FERRIS_API int ferris_moe_router(const void* x, int ldx, int dtype, const void* 
     do {                                                                                                                 \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_router_kernel<T, B>, smem)) != FERRIS_OK) return rc;        \
         ferris_launch(moe_router_kernel<T, B>, grid, block, smem, s, (const T*)x, ldx, (const T*)w, bias, ids, weights,  \
-                      tokens, width, experts, top);                                                                      \
+                      tokens, width, experts, top, scored, correction, groups, keep, with_weights, identity_w);          \
     } while (0)
     if (dtype == FERRIS_F32) {
         if (per_block) FERRIS_ROUTER_RUN(float, true); else FERRIS_ROUTER_RUN(float, false);
@@ -694,8 +818,11 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
                                               long long gate_up_stride, const void* down, const int* ids,
                                               const float* weights, void* act, float* h,
                                               int ldh, int tokens, int width, int ff, int top, int accumulate,
-                                              float* y, int experts, void* stream) {
+                                              float* y, int experts, int act_kind, float act_limit,
+                                              const float* identity_w, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
+    if (experts <= 0) FERRIS_REFUSE("experts: %d experts", experts);
+    if (act_kind < 0 || act_kind > 2) FERRIS_REFUSE("experts: unknown activation %d", act_kind);
     if (width <= 0 || ff <= 0 || top <= 0 || top > MOE_MAX_TOP) FERRIS_REFUSE("experts: width %d, ff %d, %d chosen", width, ff, top);
     if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("experts: unknown dtype %d", dtype);
     const size_t few_up = FEW_WARPS * FEW_RING_BYTES + (size_t)MOE_FEW_ROWS * width * sizeof(float);
@@ -721,7 +848,8 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_gate_up_few_kernel<T>, few_up)) != FERRIS_OK) return rc;     \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_down_few_kernel<T>, few_down)) != FERRIS_OK) return rc;      \
         ferris_launch(moe_gate_up_few_kernel<T>, grid_up, dim3(32 * FEW_WARPS), few_up, s, (const T*)x, ldx, (const T*)gate,         \
-                      (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, pairs, top, slab_up);                \
+                      (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, pairs, top, slab_up, act_kind,    \
+                      act_limit);                                                                                         \
         ferris_launch(moe_down_few_kernel<T>, grid_down, dim3(32 * FEW_WARPS), few_down, s, (const T*)act, (const T*)down, ids, y,   \
                       width, ff, pairs, slab_down);                                                                       \
     } while (0)
@@ -732,8 +860,15 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
 #undef FERRIS_MOE_FEW
         const size_t n4 = (size_t)tokens * (width / 4);
         const size_t want4 = (n4 + 255) / 256;
-        ferris_launch(moe_combine_kernel, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s,
-                      (const float*)y, width, (const int*)nullptr, weights, h, ldh, tokens, width / 4, top, accumulate);
+        const int* skip = identity_w ? ids : (const int*)nullptr;
+        if (dtype == FERRIS_F32)
+            ferris_launch(moe_combine_kernel<float>, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s,
+                          (const float*)y, width, (const int*)nullptr, weights, h, ldh, tokens, width / 4, top, accumulate,
+                          skip, experts, (const float*)x, ldx, identity_w);
+        else
+            ferris_launch(moe_combine_kernel<bf16>, dim3((unsigned)(want4 < 148 * 16 ? want4 : 148 * 16)), dim3(256), 0, s,
+                          (const float*)y, width, (const int*)nullptr, weights, h, ldh, tokens, width / 4, top, accumulate,
+                          skip, experts, (const bf16*)x, ldx, identity_w);
         FERRIS_LAUNCH_CHECK();
     }
     const size_t smem_up = (size_t)width * sizeof(float), smem_down = (size_t)top * ff * sizeof(float);
@@ -757,9 +892,10 @@ FERRIS_API int ferris_moe_experts_token_major(const void* x, int ldx, int dtype,
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_gate_up_kernel<T>, smem_up)) != FERRIS_OK) return rc;        \
         if ((rc = ferris_allow_dynamic_smem((const void*)moe_down_kernel<T>, smem_down)) != FERRIS_OK) return rc;         \
         ferris_launch(moe_gate_up_kernel<T>, dim3(grid_up.x, grid_up.y, 1), dim3(128), smem_up, s, (const T*)x, ldx,      \
-                      (const T*)gate, (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, top, slab_up);                                    \
+                      (const T*)gate, (const T*)up, (size_t)gate_up_stride, ids, (T*)act, width, ff, top, slab_up,      \
+                      experts, act_kind, act_limit);                                                                      \
         ferris_launch(moe_down_kernel<T>, grid_down, dim3(128), smem_down, s, (const T*)act, (const T*)down, ids, weights, \
-                      h, ldh, width, ff, top, slab_down, accumulate);                                                     \
+                      h, ldh, width, ff, top, slab_down, accumulate, experts, (const T*)x, ldx, identity_w);              \
     } while (0)
     if (dtype == FERRIS_F32)
         FERRIS_MOE_RUN(float);

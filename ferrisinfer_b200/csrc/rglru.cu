@@ -1,0 +1,240 @@
+// A gated linear recurrent unit over channels (the recurrence of a Griffin-style recurrent block):
+//
+//   per block n of the channels (C / blocks neighbouring channels):  r = sigmoid(Ra[n] u_n + ra_n),  i = sigmoid(Ri[n] u_n + ri_n)
+//   log a = -c * r * softplus(lam);   a = exp(log a);   s_t = a s_(t-1) + sqrt(1 - a^2) * i * u_t;   out_t = s_t * act(y_t)
+//
+// u: the step's rows after the short convolution, y: the other branch as projected (act = tanh-form GELU or
+// nothing), s: fp32 [slots, C], zero when a request is admitted.  Two kernels.
+//
+// `rglru_gates`: the two block-diagonal products with fp32 sums, the sigmoids, the decay and the input's factor, all
+// fp32: it leaves a and b = sqrt(1 - a^2) i u per (token, channel).  1 - a^2 is formed as -expm1(2 log a), so that a
+// decay close to one keeps its digits.  The matrices lie transposed ([blocks, in, out]) so that the threads of a
+// block read consecutive weights; eight tokens share one pass over them, and the inputs are cut into four runs that
+// four quarters of the block take (their sums added in the runs' order).
+//
+// `rglru_scan`: s_t = a_t s_(t-1) + b_t is linear in s, so a run of tokens is summed up by (product of its a, its end
+// value from zero) and runs combine.  A block owns 32 channels of one request and walks its tokens in tiles of
+// SEGS x SEG_TOKENS: a thread holds one run of SEG_TOKENS tokens of one channel in registers (all loads of a tile are
+// in flight together), forms the run's summary, the summaries meet in shared memory, every thread folds the runs
+// before its own onto the tile's incoming value, and then writes its tokens' outputs.  The chain of a tile is
+// SEG_TOKENS + SEGS + SEG_TOKENS steps instead of SEGS x SEG_TOKENS.  A step of single tokens is one thread per
+// (request, channel).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int RG_TOKENS = 8, RG_COLS = 64, RG_PARTS = 4, RG_THREADS = RG_COLS * RG_PARTS;
+constexpr int SCAN_CH = 32, SCAN_SEGS = 8, SCAN_SEG_TOKENS = 8, SCAN_THREADS = SCAN_CH * SCAN_SEGS;
+
+__device__ __forceinline__ float softplus_r(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float sigmoid_r(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gelu_tanh_r(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// u: [tokens, C] rows ldu apart; wa, wi: [blocks, bs, bs] as [block][input][output]; ba, bi, sp (softplus(lam)): fp32 [C].
+template <typename T>
+__global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int ldu, const T* __restrict__ wa,
+                                                                 const T* __restrict__ wi, const float* __restrict__ ba,
+                                                                 const float* __restrict__ bi, const float* __restrict__ sp,
+                                                                 float* __restrict__ a_out, float* __restrict__ b_out,
+                                                                 int tokens, int C, int bs, float decay_factor) {
+    extern __shared__ float us[];  // [RG_TOKENS][bs], then the parts' sums [RG_PARTS - 1][2][RG_TOKENS][RG_COLS]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t0 = blockIdx.x * RG_TOKENS, blk = blockIdx.y;
+    const int cl = threadIdx.x % RG_COLS, part = threadIdx.x / RG_COLS;
+    const int n = blockIdx.z * RG_COLS + cl;
+    const int rows = tokens - t0 < RG_TOKENS ? tokens - t0 : RG_TOKENS;
+    for (int i = threadIdx.x; i < RG_TOKENS * bs; i += RG_THREADS) {
+        const int r = i / bs, k = i - r * bs;
+        us[i] = r < rows ? to_float(u[(size_t)(t0 + r) * ldu + (size_t)blk * bs + k]) : 0.0f;
+    }
+    __syncthreads();
+    float acc_a[RG_TOKENS], acc_i[RG_TOKENS];
+#pragma unroll
+    for (int r = 0; r < RG_TOKENS; ++r) acc_a[r] = 0.0f, acc_i[r] = 0.0f;
+    const int per = (bs + RG_PARTS - 1) / RG_PARTS;
+    const int k0 = part * per, k1 = min(bs, k0 + per);
+    if (n < bs) {
+        const T* pa = wa + (size_t)blk * bs * bs + n;
+        const T* pi = wi + (size_t)blk * bs * bs + n;
+#pragma unroll 4
+        for (int k = k0; k < k1; ++k) {
+            const float va = to_float(pa[(size_t)k * bs]), vi = to_float(pi[(size_t)k * bs]);
+#pragma unroll
+            for (int r = 0; r < RG_TOKENS; ++r) {
+                const float x = us[r * bs + k];
+                acc_a[r] = fmaf(x, va, acc_a[r]), acc_i[r] = fmaf(x, vi, acc_i[r]);
+            }
+        }
+    }
+    float* sums = us + RG_TOKENS * bs;
+    if (part > 0) {
+#pragma unroll
+        for (int r = 0; r < RG_TOKENS; ++r) {
+            sums[(((part - 1) * 2 + 0) * RG_TOKENS + r) * RG_COLS + cl] = acc_a[r];
+            sums[(((part - 1) * 2 + 1) * RG_TOKENS + r) * RG_COLS + cl] = acc_i[r];
+        }
+    }
+    __syncthreads();
+    if (part > 0 || n >= bs) return;
+    const int c = blk * bs + n;
+    const float bias_a = ba[c], bias_i = bi[c], rate = decay_factor * sp[c];
+#pragma unroll
+    for (int r = 0; r < RG_TOKENS; ++r) {
+        if (r >= rows) break;
+        float za = acc_a[r], zi = acc_i[r];
+#pragma unroll
+        for (int p = 0; p < RG_PARTS - 1; ++p) {  // in the runs' order
+            za += sums[((p * 2 + 0) * RG_TOKENS + r) * RG_COLS + cl];
+            zi += sums[((p * 2 + 1) * RG_TOKENS + r) * RG_COLS + cl];
+        }
+        const float log_a = -rate * sigmoid_r(za + bias_a);
+        const float gate = sigmoid_r(zi + bias_i);
+        const size_t at = (size_t)(t0 + r) * C + c;
+        a_out[at] = expf(log_a);
+        b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gate * us[r * bs + n];
+    }
+}
+
+// a, b: fp32 [tokens, C]; y: [tokens, C] rows ldy apart (null: the state itself is the output); out: rows ldo apart.
+template <typename T>
+__global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(const float* a, const float* b, const T* y, int ldy,
+                                                                  T* __restrict__ out, int ldo, float* state,
+                                                                  const int* __restrict__ seq_q_start,
+                                                                  const int* __restrict__ seq_state_slot, int C, int act,
+                                                                  int write_state) {
+    __shared__ float prod[SCAN_SEGS][SCAN_CH], last[SCAN_SEGS][SCAN_CH], carry[SCAN_CH];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x;
+    const int lane = threadIdx.x % SCAN_CH, seg = threadIdx.x / SCAN_CH;
+    const int c = blockIdx.y * SCAN_CH + lane;
+    const bool live = c < C;
+    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    if (row1 <= row0) return;
+    float* S = state + (size_t)seq_state_slot[seq] * C + (live ? c : 0);
+    if (seg == 0) carry[lane] = live ? *S : 0.0f;
+    constexpr int TILE = SCAN_SEGS * SCAN_SEG_TOKENS;
+    for (int t0 = row0; t0 < row1; t0 += TILE) {
+        const int first = t0 + seg * SCAN_SEG_TOKENS;
+        float av[SCAN_SEG_TOKENS], bv[SCAN_SEG_TOKENS];
+#pragma unroll
+        for (int j = 0; j < SCAN_SEG_TOKENS; ++j) {
+            const bool in = live && first + j < row1;
+            av[j] = in ? a[(size_t)(first + j) * C + c] : 1.0f;
+            bv[j] = in ? b[(size_t)(first + j) * C + c] : 0.0f;
+        }
+        float p = 1.0f, s = 0.0f;  // the run from zero: its product of decays and its end value
+#pragma unroll
+        for (int j = 0; j < SCAN_SEG_TOKENS; ++j) p *= av[j], s = fmaf(av[j], s, bv[j]);
+        prod[seg][lane] = p, last[seg][lane] = s;
+        __syncthreads();  // also: the carry of the tile before (or the state) is written
+        float in_value = carry[lane];
+        for (int g = 0; g < seg; ++g) in_value = fmaf(prod[g][lane], in_value, last[g][lane]);
+        s = in_value;
+#pragma unroll
+        for (int j = 0; j < SCAN_SEG_TOKENS; ++j) {
+            s = fmaf(av[j], s, bv[j]);
+            if (live && first + j < row1) {
+                float v = s;
+                if (y) {
+                    const float z = to_float(y[(size_t)(first + j) * ldy + c]);
+                    v *= act ? gelu_tanh_r(z) : z;
+                }
+                out[(size_t)(first + j) * ldo + c] = from_float<T>(v);
+            }
+        }
+        __syncthreads();  // everyone has read the carry and the summaries
+        if (seg == SCAN_SEGS - 1) carry[lane] = s;  // rows beyond the step's end pass the value on (a = 1, b = 0)
+    }
+    __syncthreads();
+    if (write_state && live && seg == 0) *S = carry[lane];
+}
+
+// A step in which every request brings one token: a thread per (request, channel).
+template <typename T>
+__global__ void __launch_bounds__(256) rglru_scan_single_kernel(const float* a, const float* b, const T* y, int ldy,
+                                                                T* __restrict__ out, int ldo, float* state,
+                                                                const int* __restrict__ seq_state_slot, int C, int act,
+                                                                int write_state) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float* S = state + (size_t)seq_state_slot[t] * C + c;
+    const float s = fmaf(a[(size_t)t * C + c], *S, b[(size_t)t * C + c]);
+    if (write_state) *S = s;
+    float v = s;
+    if (y) {
+        const float z = to_float(y[(size_t)t * ldy + c]);
+        v *= act ? gelu_tanh_r(z) : z;
+    }
+    out[(size_t)t * ldo + c] = from_float<T>(v);
+}
+
+}  // namespace
+
+// u: [tokens, C] in the activations' type, rows ldu apart; wa, wi: [blocks, C / blocks, C / blocks] in the same type,
+// TRANSPOSED ([block][input][output]); ba, bi, sp: fp32 [C] (sp = softplus of the decay's parameter); a_out, b_out: fp32
+// [tokens, C]; decay_factor: the constant c of log a = -c r softplus(lam).
+FERRIS_API int ferris_rglru_gates(const void* u, int ldu, int dtype, const void* wa, const void* wi, const float* ba,
+                                  const float* bi, const float* sp, float* a_out, float* b_out, int tokens, int C,
+                                  int blocks, float decay_factor, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (C <= 0 || blocks <= 0 || C % blocks || blocks > 65535) FERRIS_REFUSE("recurrent unit gates: %d channels in %d blocks", C, blocks);
+    const int bs = C / blocks;
+    const size_t smem = ((size_t)RG_TOKENS * bs + (size_t)(RG_PARTS - 1) * 2 * RG_TOKENS * RG_COLS) * sizeof(float);
+    if (smem > 200 * 1024) FERRIS_REFUSE("recurrent unit gates: blocks of %d channels are more than shared memory holds", bs);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((tokens + RG_TOKENS - 1) / RG_TOKENS, blocks, (bs + RG_COLS - 1) / RG_COLS), block(RG_THREADS);
+    if (dtype == FERRIS_F32) {
+        int e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_kernel<float>, smem);
+        if (e_ != FERRIS_OK) return e_;
+        ferris_launch(rglru_gates_kernel<float>, grid, block, smem, s, (const float*)u, ldu, (const float*)wa, (const float*)wi,
+                      ba, bi, sp, a_out, b_out, tokens, C, bs, decay_factor);
+    } else if (dtype == FERRIS_BF16) {
+        int e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_kernel<bf16>, smem);
+        if (e_ != FERRIS_OK) return e_;
+        ferris_launch(rglru_gates_kernel<bf16>, grid, block, smem, s, (const bf16*)u, ldu, (const bf16*)wa, (const bf16*)wi, ba,
+                      bi, sp, a_out, b_out, tokens, C, bs, decay_factor);
+    } else
+        FERRIS_REFUSE("recurrent unit gates: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// a, b: fp32 [tokens, C]; y (may be null), out: the activations' type, rows ldy / ldo apart; state: fp32 [slots, C];
+// act: 1 = the tanh form of GELU on y, 0 = y as it is.  single_tokens: every request brings one row (row t of request t).
+FERRIS_API int ferris_rglru_scan(const float* a, const float* b, const void* y, int ldy, void* out, int ldo, int dtype,
+                                 float* state, const int* seq_q_start, const int* seq_state_slot, int tokens, int seqs,
+                                 int C, int act, int write_state, int single_tokens, void* stream) {
+    if (tokens <= 0 || seqs <= 0) return FERRIS_OK;
+    if (C <= 0 || !a || !b || !state || !out) FERRIS_REFUSE("recurrent unit scan: %d channels, or a tensor is missing", C);
+    if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("recurrent unit scan: unknown dtype %d", dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (single_tokens && tokens == seqs) {
+        const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
+        const dim3 grid(tokens, (C + threads - 1) / threads);
+        if (grid.y > 65535) FERRIS_REFUSE("recurrent unit scan: %d channels are more than one launch takes", C);
+        if (dtype == FERRIS_F32)
+            ferris_launch(rglru_scan_single_kernel<float>, grid, dim3(threads), 0, s, a, b, (const float*)y, ldy, (float*)out, ldo,
+                          state, seq_state_slot, C, act, write_state);
+        else
+            ferris_launch(rglru_scan_single_kernel<bf16>, grid, dim3(threads), 0, s, a, b, (const bf16*)y, ldy, (bf16*)out, ldo,
+                          state, seq_state_slot, C, act, write_state);
+        FERRIS_LAUNCH_CHECK();
+    }
+    const dim3 grid(seqs, (C + SCAN_CH - 1) / SCAN_CH);
+    if (grid.y > 65535) FERRIS_REFUSE("recurrent unit scan: %d channels are more than one launch takes", C);
+    if (dtype == FERRIS_F32)
+        ferris_launch(rglru_scan_kernel<float>, grid, dim3(SCAN_THREADS), 0, s, a, b, (const float*)y, ldy, (float*)out, ldo,
+                      state, seq_q_start, seq_state_slot, C, act, write_state);
+    else
+        ferris_launch(rglru_scan_kernel<bf16>, grid, dim3(SCAN_THREADS), 0, s, a, b, (const bf16*)y, ldy, (bf16*)out, ldo,
+                      state, seq_q_start, seq_state_slot, C, act, write_state);
+    FERRIS_LAUNCH_CHECK();
+}

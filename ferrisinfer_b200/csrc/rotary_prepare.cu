@@ -203,6 +203,72 @@ __global__ void __launch_bounds__(256) qk_norm_rotary_cache_write_paired_kernel(
     }
 }
 
+// The norm per HEAD: every q and k head divided by the root mean square of its own d elements and multiplied by a
+// weight of d numbers that all heads share (wq for queries, wk for keys; null: that side is not normed), then rotated
+// and stored as above.  A warp per head: its lanes sum the head's squares, then norm, rotate and store it; the values
+// are copied by the whole block.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_head_norm_rotary_cache_write_kernel(
+    T* qkv, int ld, const int* __restrict__ positions, const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int nh, int nkv, int d, int dv, int page_size, const float* __restrict__ q_weight,
+    const float* __restrict__ k_weight, float eps, const float* __restrict__ freq, int rotary, int interleaved, float mag,
+    int write_kv) {
+    extern __shared__ float cs[];  // the token's cosines, then its sines, both times mag
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary >> 1;
+    for (int f = threadIdx.x; f < half; f += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * freq[f], &s, &c);
+        cs[f] = c * mag, cs[half + f] = s * mag;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * ld;
+    const int nq = nh * d, nk = nkv * d;
+    const int slot = write_kv ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int in_page = slot >= 0 ? slot % page_size : 0;
+    if (slot >= 0) {
+        const T* vrow = row + nq + nk;
+        for (int e = threadIdx.x; e < nkv * dv; e += blockDim.x) {
+            const int h = e / dv, i = e - h * dv;
+            v_cache[(((size_t)page * nkv + h) * page_size + in_page) * dv + i] = vrow[e];
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int heads = slot >= 0 ? nh + nkv : nh;  // without a cache to write, the keys are left alone
+    for (int head = warp; head < heads; head += warps) {
+        const bool is_q = head < nh;
+        const int h = is_q ? head : head - nh;
+        const float* w = is_q ? q_weight : k_weight;
+        const T* src = row + (size_t)head * d;
+        T* dst = is_q ? row + (size_t)head * d : k_cache + (((size_t)page * nkv + h) * page_size + in_page) * d;
+        float inv = 1.0f;
+        if (w) {
+            float ss = 0.0f;
+            for (int i = lane; i < d; i += 32) {
+                const float x = to_float(src[i]);
+                ss = fmaf(x, x, ss);
+            }
+            inv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);  // every lane has read the head before any lane writes it
+        }
+        for (int j = lane; j < half; j += 32) {
+            const int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + half;
+            float u = to_float(src[i0]), v = to_float(src[i1]);
+            if (w) u = (u * inv) * w[i0], v = (v * inv) * w[i1];
+            const float c = cs[j], s = cs[half + j];
+            dst[i0] = from_float<T>(u * c - v * s);
+            dst[i1] = from_float<T>(v * c + u * s);
+        }
+        for (int i = rotary + lane; i < d; i += 32) {
+            const float x = to_float(src[i]);
+            dst[i] = from_float<T>(w ? (x * inv) * w[i] : x);
+        }
+    }
+}
+
 }  // namespace
 
 FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, const int* positions,
@@ -248,5 +314,34 @@ FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, c
                       freq, rotary, interleaved, mag, values_from_keys, write_kv);
     else
         FERRIS_REFUSE("qk norm + rotation: unknown dtype %d", dtype);
+    FERRIS_LAUNCH_CHECK();
+}
+
+// As above with the norm taken per head: q_weight, k_weight fp32 [d] (shared by the heads; null: no norm on that side).
+FERRIS_API int ferris_qk_head_norm_rotary_cache_write(void* qkv, int ld, int dtype, const int* positions,
+                                                      const int* slot_mapping, void* k_cache, void* v_cache, int tokens,
+                                                      int nh, int nkv, int d, int dv, int page_size, const float* q_weight,
+                                                      const float* k_weight, float eps, const float* freq, int rotary,
+                                                      int interleaved, float mag, int write_kv, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0)
+        FERRIS_REFUSE("head norm + rotation: nh=%d nkv=%d d=%d dv=%d page_size=%d", nh, nkv, d, dv, page_size);
+    if (rotary < 0 || rotary > d || (rotary & 1) || (rotary > 0 && !freq))
+        FERRIS_REFUSE("head norm + rotation: %d rotated elements of heads of %d", rotary, d);
+    if (ld < (nh + nkv) * d + nkv * dv) FERRIS_REFUSE("head norm + rotation: rows of %d are too short", ld);
+    if (write_kv && (!slot_mapping || !k_cache || !v_cache)) FERRIS_REFUSE("head norm + rotation: no cache to write");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)(rotary > 0 ? rotary : 1) * sizeof(float);
+    const int threads = (nh + nkv) >= 8 ? 256 : 128;
+    if (dtype == FERRIS_F32)
+        ferris_launch(qk_head_norm_rotary_cache_write_kernel<float>, dim3(tokens), dim3(threads), smem, s, (float*)qkv, ld,
+                      positions, slot_mapping, (float*)k_cache, (float*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight,
+                      eps, freq, rotary, interleaved, mag, write_kv);
+    else if (dtype == FERRIS_BF16)
+        ferris_launch(qk_head_norm_rotary_cache_write_kernel<bf16>, dim3(tokens), dim3(threads), smem, s, (bf16*)qkv, ld,
+                      positions, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps,
+                      freq, rotary, interleaved, mag, write_kv);
+    else
+        FERRIS_REFUSE("head norm + rotation: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
 }

@@ -35,6 +35,13 @@ FERRIS_API void ferris_gemm_set_activation(int kind, float a, float b) {
     g_epilogue_act.a = a;
     g_epilogue_act.b = b;
 }
+// The gated activation (ferris_gated_act) that the next product of two accumulators applies; kind 0 (SiLU) is what
+// those products do anyway.
+FERRIS_API void ferris_gemm_set_gated_activation(int kind, float limit) {
+    g_epilogue_act.kind = kind ? FERRIS_EPILOGUE_GATED + kind : 0;
+    g_epilogue_act.a = limit;
+    g_epilogue_act.b = 0.0f;
+}
 FerrisEpilogueAct ferris_take_epilogue_act() {
     const FerrisEpilogueAct e = g_epilogue_act;
     g_epilogue_act.kind = 0;

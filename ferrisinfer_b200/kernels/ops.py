@@ -587,6 +587,81 @@ def gemm_swiglu(x, gate_up_weight, out, workspace=None):
     swiglu(gate_up, out)
 
 
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+_set_gated = None
+
+
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: float = 0.0):
+    """out[t, j] = f(gate_up[t, j], gate_up[t, I + j]): f = silu(g) u, gelu_tanh(g) u, or ("clamped_swish", with
+    ``limit`` L) min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1); fp32 arithmetic."""
+    T, I = out.shape
+    T2, W2, ld = _rows(gate_up, "gated activation input")
+    _need(out, "gated activation output", gate_up.dtype)
+    if kind not in GATED_ACTIVATIONS or T2 != T or W2 != 2 * I:
+        raise KernelError(f"gated activation '{kind}': input {tuple(gate_up.shape)}, output {tuple(out.shape)}")
+    _check(_lib().ferris_gated_activation(_ptr(gate_up), _c_int(ld), _ptr(out), _c_int(_dt(out, "gated activation")), _c_int(T),
+                                          _c_int(I), _c_int(GATED_ACTIVATIONS[kind]), _c_float(limit), _stream()),
+           "gated activation")
+
+
+def gemm_gated(x, gate_up_weight, out, kind: str = "silu", limit: float = 0.0, workspace=None):
+    """out [T, I] = f(x Wg^T, x Wu^T) with gate_up_weight = [Wg; Wu] ([2I, K]) and f a gated activation (see
+    ``gated_activation``).  "silu" is ``gemm_swiglu``.  The others in bf16: the weight-stationary kernel (at most 16
+    tokens) and the tcgen05 kernels of long steps apply f to the two fp32 accumulators in their epilogue; anything else
+    is the product followed by the activation kernel."""
+    global _set_gated
+    if kind == "silu":
+        return gemm_swiglu(x, gate_up_weight, out, workspace)
+    if kind not in GATED_ACTIVATIONS:
+        raise KernelError(f"gated activation '{kind}' is not known ({', '.join(GATED_ACTIVATIONS)})")
+    T, I = out.shape
+    if gate_up_weight.shape[0] != 2 * I:
+        raise KernelError(f"gemm_gated: weight {tuple(gate_up_weight.shape)} for {I} outputs")
+    if out.dtype == torch.bfloat16:
+        if _set_gated is None:
+            _set_gated = _lib().ferris_gemm_set_gated_activation
+            _set_gated.argtypes = [_I, _F]
+            _set_gated.restype = None
+        code = GATED_ACTIVATIONS[kind]
+        try:  # the product that is launched next takes the activation; whatever happens, none is left behind
+            if T <= 16 and gemm_skinny_enabled() and _skinny_takes(x, gate_up_weight, out, 2):
+                _set_gated(code, float(limit))
+                gemm_skinny(x, gate_up_weight, None, out, 3, up_row_offset=I)
+                return
+            if isinstance(x, LazyRMSNorm):
+                x = x.materialize()
+            if tensor_core_gemm_takes(x, gate_up_weight) and _lib().ferris_gemm_tcgen05_fuses_gated_activation(
+                    _c_int(T), _c_int(I), _c_int(x.shape[1]), _c_int(out.stride(0)), _ptr(out)):
+                _set_gated(code, float(limit))
+                gemm_tcgen05(x, gate_up_weight, None, out, 3, up_row_offset=I)
+                return
+        finally:
+            _set_gated(0, 0.0)
+    if workspace is not None:
+        gate_up = workspace.get("ffn_gate_up", (T, 2 * I), out.dtype)
+    else:
+        gate_up = torch.empty(T, 2 * I, dtype=out.dtype, device=out.device)
+    gemm(x, gate_up_weight, None, gate_up)
+    gated_activation(gate_up, out, kind, limit)
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, kind: str = "sigmoid", scale: float = 1.0):
+    """out = x * a(gate) * scale element by element, a = sigmoid or SiLU; fp32 arithmetic; ``out`` may be ``x``."""
+    T, n, ldx = _rows(x, "gated rows")
+    T2, n2, ldg = _rows(gate, "gate")
+    T3, n3, ldo = _rows(out, "gated output")
+    if (T2, n2) != (T, n) or (T3, n3) != (T, n) or gate.dtype != x.dtype or out.dtype != x.dtype or kind not in ("sigmoid", "silu"):
+        raise KernelError(f"gate '{kind}': x {tuple(x.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}")
+    _check(_lib().ferris_gate_mul(_ptr(x), _c_int(ldx), _ptr(gate), _c_int(ldg), _ptr(out), _c_int(ldo), _c_int(_dt(x, "gate")),
+                                  _c_int(T), _c_int(n), _c_int(1 if kind == "silu" else 0), _c_float(scale), _stream()), "gate")
+
+
+def scale_(x: torch.Tensor, scale: float):
+    """x <- x * scale in place; fp32."""
+    _need(x, "rows to scale", torch.float32)
+    _check(_lib().ferris_scale(_ptr(x), ctypes.c_longlong(x.numel()), _c_float(scale), _stream()), "scale")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor):
     """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
     _need(gate_up, "swiglu input")
@@ -1109,6 +1184,83 @@ def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torc
     )
 
 
+def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_z: torch.Tensor, power: float,
+                         out: torch.Tensor, state: torch.Tensor, ctx, num_heads: int, head_dim: int, v_head_dim: int,
+                         q_scale: float = 1.0, write_state: bool = True):
+    """Linear attention with a decay per key channel that changes with every token: per head
+    S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = q_scale S_t^T q_t, alpha_t = sigmoid(row_z[t])^power (fp32, formed in
+    the kernel).  q, k: [T, heads x dim], v: [T, heads x vdim] (views with contiguous rows); row_z fp32 [T, heads x dim];
+    out fp32 [T, heads x vdim]; state fp32 [slots, heads, vdim, dim] (transposed), carried in the requests' slots."""
+    T, wq, ldq = _rows(q, "recurrence q")
+    _, wk, ldk = _rows(k, "recurrence k")
+    _, wv, ldv = _rows(v, "recurrence v")
+    _, wz, ldz = _rows(row_z, "recurrence decays")
+    _, wo, ldo = _rows(out, "recurrence output")
+    _need(state, "recurrent state", torch.float32)
+    if (wq != num_heads * head_dim or wk != wq or wz != wq or wv != num_heads * v_head_dim or wo != wv
+            or row_z.dtype != torch.float32 or out.dtype != torch.float32 or k.dtype != q.dtype or v.dtype != q.dtype
+            or state.shape[1:] != (num_heads, v_head_dim, head_dim)):
+        raise KernelError(f"row-decay recurrence: q {tuple(q.shape)}, v {tuple(v.shape)}, decays {tuple(row_z.shape)}, "
+                          f"state {tuple(state.shape)}")
+    _check(
+        _lib().ferris_row_decay_recurrence(_ptr(q), _c_int(ldq), _ptr(k), _c_int(ldk), _ptr(v), _c_int(ldv),
+                                           _c_int(_dt(q, "recurrence")), _ptr(row_z), _c_int(ldz), _c_float(power),
+                                           _c_float(q_scale), _ptr(out), _c_int(ldo), _ptr(state), _ptr(ctx.seq_q_start),
+                                           _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs), _c_int(num_heads),
+                                           _c_int(head_dim), _c_int(v_head_dim), _c_int(1 if write_state else 0),
+                                           _c_int(int(getattr(ctx, "max_q_len", 0))), _stream()),
+        "row-decay recurrence",
+    )
+
+
+def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
+                softplus_lam: torch.Tensor, a_out: torch.Tensor, b_out: torch.Tensor, decay_factor: float):
+    """The gates of a gated linear recurrent unit: per block n of the channels r = sigmoid(Ra[n] u_n + ba),
+    i = sigmoid(Ri[n] u_n + bi); a = exp(-decay_factor r softplus_lam); b = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t``:
+    [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out, b_out fp32 [T, C]."""
+    T, C, ldu = _rows(u, "recurrent unit input")
+    _need(wa_t, "recurrence gate matrices", u.dtype)
+    _need(wi_t, "input gate matrices", u.dtype)
+    blocks = wa_t.shape[0]
+    bs = C // max(blocks, 1)
+    for t_, name in ((ba, "recurrence gate bias"), (bi, "input gate bias"), (softplus_lam, "decay rates")):
+        _need(t_, name, torch.float32)
+    _need(a_out, "decays", torch.float32)
+    _need(b_out, "gated inputs", torch.float32)
+    if (wa_t.shape != (blocks, bs, bs) or wi_t.shape != wa_t.shape or blocks * bs != C or ba.numel() != C or bi.numel() != C
+            or softplus_lam.numel() != C or a_out.shape != (T, C) or b_out.shape != (T, C)):
+        raise KernelError(f"recurrent unit gates: u {tuple(u.shape)}, matrices {tuple(wa_t.shape)}")
+    _check(_lib().ferris_rglru_gates(_ptr(u), _c_int(ldu), _c_int(_dt(u, "recurrent unit")), _ptr(wa_t), _ptr(wi_t), _ptr(ba),
+                                     _ptr(bi), _ptr(softplus_lam), _ptr(a_out), _ptr(b_out), _c_int(T), _c_int(C),
+                                     _c_int(blocks), _c_float(decay_factor), _stream()), "recurrent unit gates")
+
+
+def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], out: torch.Tensor, state: torch.Tensor, ctx,
+               gelu: bool = True, write_state: bool = True):
+    """s_t = a_t s_(t-1) + b_t per (request, channel) from the request's slot of ``state`` (fp32 [slots, C]);
+    out_t = s_t * act(y_t), act the tanh form of GELU (``gelu``) or nothing; without ``y`` the state itself.  a, b fp32
+    [T, C]; y, out in the activations' type (views with contiguous rows)."""
+    _need(a, "decays", torch.float32)
+    _need(b, "gated inputs", torch.float32)
+    _need(state, "recurrent state", torch.float32)
+    T, C = a.shape
+    T2, C2, ldo = _rows(out, "recurrent unit output")
+    ldy = 0
+    if y is not None:
+        T3, C3, ldy = _rows(y, "recurrent unit branch")
+        if (T3, C3) != (T, C) or y.dtype != out.dtype:
+            raise KernelError(f"recurrent unit scan: branch {tuple(y.shape)} for {T} x {C}")
+    if b.shape != (T, C) or (T2, C2) != (T, C) or state.dim() != 2 or state.shape[1] != C:
+        raise KernelError(f"recurrent unit scan: a {tuple(a.shape)}, b {tuple(b.shape)}, out {tuple(out.shape)}, "
+                          f"state {tuple(state.shape)}")
+    single = bool(getattr(ctx, "max_q_len", 0) == 1 and T == ctx.num_seqs)
+    _check(_lib().ferris_rglru_scan(_ptr(a), _ptr(b), _ptr(y), _c_int(ldy), _ptr(out), _c_int(ldo),
+                                    _c_int(_dt(out, "recurrent unit")), _ptr(state), _ptr(ctx.seq_q_start),
+                                    _ptr(ctx.seq_state_slot), _c_int(T), _c_int(ctx.num_seqs), _c_int(C),
+                                    _c_int(1 if gelu else 0), _c_int(1 if write_state else 0), _c_int(1 if single else 0),
+                                    _stream()), "recurrent unit scan")
+
+
 def streams_expand(h: torch.Tensor, xs: torch.Tensor, streams: int):
     """xs [T, streams x W] = ``streams`` copies of every row of h [T, W]; both fp32."""
     _need(h, "residual rows", torch.float32)
@@ -1330,17 +1482,22 @@ def softcap_(logits: torch.Tensor, cap: float):
 def qk_norm_rotary_cache_write(qkv: torch.Tensor, ctx, slot_mapping: Optional[torch.Tensor], k_cache, v_cache,
                                num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
                                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
-                               rotary: Optional[RotaryTable], values_from_keys: bool = False, write_kv: bool = True):
+                               rotary: Optional[RotaryTable], values_from_keys: bool = False, write_kv: bool = True,
+                               per_head: bool = False):
     """Between the q/k(/v) product and attention: q and k each divided by the root mean square of their WHOLE projection
     (all heads at once) and multiplied by ``q_norm`` / ``k_norm`` (fp32, one number per element; None: no norm), then
     rotated by the tokens' positions; q rewritten in place, k and the values into the paged cache.
     ``values_from_keys``: the values are the keys as projected (before norm and rotation); the rows then hold
-    [nh d | nkv d] only."""
+    [nh d | nkv d] only.  ``per_head``: every head is divided by the root mean square of its own elements instead, and
+    the weights hold ``head_dim`` numbers that all heads share (not with ``values_from_keys``)."""
     T, width, ld = _rows(qkv, "qkv")
     want = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * v_head_dim)
     if width != want:
         raise KernelError(f"qk norm + rotation: rows of {width} for {num_heads}+{num_kv_heads} heads of {head_dim}")
-    for name, t_, n in (("q norm weight", q_norm, num_heads * head_dim), ("k norm weight", k_norm, num_kv_heads * head_dim)):
+    if per_head and values_from_keys:
+        raise KernelError("qk norm + rotation: the norm per head does not go with values taken from the keys")
+    for name, t_, n in (("q norm weight", q_norm, head_dim if per_head else num_heads * head_dim),
+                        ("k norm weight", k_norm, head_dim if per_head else num_kv_heads * head_dim)):
         if t_ is not None:
             _need(t_, name, torch.float32)
             if t_.numel() != n:
@@ -1356,6 +1513,16 @@ def qk_norm_rotary_cache_write(qkv: torch.Tensor, ctx, slot_mapping: Optional[to
             raise KernelError(f"qk norm + rotation: caches {tuple(k_cache.shape)} {tuple(v_cache.shape)} do not fit")
     positions, freq, rdim, inter, mag = _rotary_args(rotary, ctx, head_dim, qkv.device)
     _need(ctx.positions, "positions", torch.int32)
+    if per_head:
+        _check(
+            _lib().ferris_qk_head_norm_rotary_cache_write(
+                _ptr(qkv), _c_int(ld), _c_int(_dt(qkv, "qkv")), _ptr(ctx.positions), _ptr(slot_mapping if write_kv else None),
+                _ptr(k_cache if write_kv else None), _ptr(v_cache if write_kv else None), _c_int(T), _c_int(num_heads),
+                _c_int(num_kv_heads), _c_int(head_dim), _c_int(v_head_dim), _c_int(page_size), _ptr(q_norm), _ptr(k_norm),
+                _c_float(eps), freq, rdim, inter, mag, _c_int(1 if write_kv else 0), _stream()),
+            "head norm + rotation + cache write",
+        )
+        return
     _check(
         _lib().ferris_qk_norm_rotary_cache_write(
             _ptr(qkv), _c_int(ld), _c_int(_dt(qkv, "qkv")), _ptr(ctx.positions), _ptr(slot_mapping if write_kv else None),
@@ -1368,9 +1535,14 @@ def qk_norm_rotary_cache_write(qkv: torch.Tensor, ctx, slot_mapping: Optional[to
 
 
 def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
-               weights: torch.Tensor, top: int):
+               weights: torch.Tensor, top: int, scored: Optional[dict] = None):
     """The ``top`` experts of every row of ``x`` and their weights: logits x weight^T + bias in fp32 sums, the largest
-    ``top`` (lowest index among equals), softmax over those alone.  ids int32 [T, top], weights fp32 [T, top]."""
+    ``top`` (lowest index among equals), softmax over those alone.  ids int32 [T, top], weights fp32 [T, top].
+    ``scored`` = {"correction": fp32 [E] or None, "groups": n, "keep": n, "with_weights": n, "identity_w": fp32 [T] or
+    None}: the scores are the softmax over ALL outputs, the choice is made by score + correction among the outputs of the
+    ``keep`` groups (of ``groups`` equal groups of neighbours) whose best choice score is largest, and the weights are
+    the chosen scores divided by their sum + 1e-20; outputs from ``with_weights`` on are identity experts, which come
+    out as the index ``with_weights`` and whose weights are summed per token into ``identity_w``."""
     T, W, ldx = _rows(x, "router input")
     _need(weight, "router matrix", x.dtype)
     _need(ids, "expert ids", torch.int32)
@@ -1380,8 +1552,22 @@ def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
         raise KernelError(f"router: x {tuple(x.shape)}, matrix {tuple(weight.shape)}, ids {tuple(ids.shape)}")
     if bias is not None:
         _need(bias, "router bias", torch.float32)
+    corr = idw = None
+    groups = keep = 1
+    real = E
+    if scored is not None:
+        corr, idw = scored.get("correction"), scored.get("identity_w")
+        groups, keep, real = int(scored.get("groups", 1)), int(scored.get("keep", 1)), int(scored.get("with_weights", E))
+        if corr is not None:
+            _need(corr, "router correction", torch.float32)
+        if idw is not None:
+            _need(idw, "identity weights", torch.float32)
+        if (corr is not None and corr.numel() != E) or (idw is not None and idw.numel() != T) or (real < E and idw is None):
+            raise KernelError(f"router: correction / identity weights do not fit {E} outputs and {T} rows")
     _check(_lib().ferris_moe_router(_ptr(x), _c_int(ldx), _c_int(_dt(x, "router")), _ptr(weight), _ptr(bias), _ptr(ids),
-                                    _ptr(weights), _c_int(T), _c_int(W), _c_int(E), _c_int(top), _stream()), "router")
+                                    _ptr(weights), _c_int(T), _c_int(W), _c_int(E), _c_int(top),
+                                    _c_int(0 if scored is None else 1), _ptr(corr), _c_int(groups), _c_int(keep), _c_int(real),
+                                    _ptr(idw), _stream()), "router")
 
 
 MOE_FEW_MAX_PAIRS = 1024  # up to here the token-major form reads an expert's weights once for all its tokens
@@ -1389,15 +1575,24 @@ MOE_GROUPED_MIN_TOKENS = 17  # from here on (bf16) the experts' rows are sorted 
 
 
 def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                h: torch.Tensor, workspace=None, accumulate: bool = True, grouped: Optional[bool] = None):
+                h: torch.Tensor, workspace=None, accumulate: bool = True, grouped: Optional[bool] = None,
+                activation: str = "silu", limit: float = 0.0, identity_w: Optional[torch.Tensor] = None):
     """h (+)= sum over a row's chosen experts of weight x down_e (silu(gate_e x) * (up_e x)).  gate_up [E, 2 ff, W] (an
     expert's gate rows, then its up rows), down [E, W, ff] in x's type; ids int32 and weights fp32 [T, top]; h fp32
     [T, W].  Steps of few tokens (up to MOE_FEW_MAX_PAIRS choices): a block per (expert, slab of rows) reads the weights
     once for all tokens that chose the expert.  More choices in 32-bit: a block per (token, chosen expert).  Both form
     whole dot products in the same order, so a token's result has the same bits.  Longer steps in bf16 (``grouped``; None = decide by size and alignment): the pairs sorted by expert, two
     tensor-core products over tiles that each meet their own expert's weights, and a pass that adds a token's results
-    in the order of its choices."""
+    in the order of its choices.  ``activation``, ``limit``: the experts' gated activation (see ``gated_activation``).
+    ``identity_w`` fp32 [T]: ids may then hold E, an expert that meets no weights, and h also gets identity_w[t] x[t]."""
     T, W, ldx = _rows(x, "experts input")
+    if activation not in GATED_ACTIVATIONS:
+        raise KernelError(f"experts: activation '{activation}' is not known ({', '.join(GATED_ACTIVATIONS)})")
+    act_kind = GATED_ACTIVATIONS[activation]
+    if identity_w is not None:
+        _need(identity_w, "identity weights", torch.float32)
+        if identity_w.numel() != T:
+            raise KernelError(f"experts: {identity_w.numel()} identity weights for {T} rows")
     T2, W2, ldh = _rows(h, "experts output")
     _need(gate_up, "gate and up matrices", x.dtype)
     _need(down, "down matrices", x.dtype)
@@ -1418,7 +1613,7 @@ def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids:
     if grouped:
         if not can_group:
             raise KernelError("experts: the sorted form takes bf16 rows of multiples of 8 elements that start on 16 bytes")
-        rows = _lib().ferris_moe_sorted_rows(_c_int(T), _c_int(top), _c_int(E))
+        rows = _lib().ferris_moe_sorted_rows(_c_int(T), _c_int(top), _c_int(E + (1 if identity_w is not None else 0)))
         if rows <= 0:
             raise KernelError(f"experts: {T} tokens x {top} choices are more than one launch takes")
         pos = get("moe_pos", (T * top,), torch.int32)
@@ -1430,7 +1625,8 @@ def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids:
         _check(_lib().ferris_moe_experts_grouped(_ptr(x), _c_int(ldx), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights),
                                                  _ptr(h), _c_int(ldh), _c_int(T), _c_int(W), _c_int(ff), _c_int(top),
                                                  _c_int(E), _c_int(rows), _ptr(pos), _ptr(row_token), _ptr(tile_expert),
-                                                 _ptr(xs), _ptr(act), _ptr(y), _c_int(1 if accumulate else 0), _stream()),
+                                                 _ptr(xs), _ptr(act), _ptr(y), _c_int(1 if accumulate else 0),
+                                                 _c_int(act_kind), _c_float(limit), _ptr(identity_w), _stream()),
                "experts (sorted)", 5)
         return
     act = get("moe_act", (T * top, ff), x.dtype)
@@ -1442,7 +1638,8 @@ def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids:
                                                  ctypes.c_longlong(2 * ff * W), _ptr(down), _ptr(ids), _ptr(weights),
                                                  _ptr(act), _ptr(h), _c_int(ldh), _c_int(T), _c_int(W), _c_int(ff),
                                                  _c_int(top), _c_int(1 if accumulate else 0),
-                                                 _ptr(y) if few else ctypes.c_void_p(0), _c_int(E), _stream()),
+                                                 _ptr(y) if few else ctypes.c_void_p(0), _c_int(E), _c_int(act_kind),
+                                                 _c_float(limit), _ptr(identity_w), _stream()),
            "experts", 3 if few else 2)
 
 

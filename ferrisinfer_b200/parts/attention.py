@@ -25,7 +25,14 @@ Options beyond the reference's layer, each a parameter of its own:
   ``values_from_keys``  there is no value matrix: a token's values are its keys as projected (before any norm or rotation)
   ``qk_norm``           {"eps", "q", "k"}: q and k each divided by sqrt(mean(.^2) + eps) over their WHOLE projection (all
                         heads at once) and multiplied by the weights named ``q`` and ``k`` under the prefix (one number
-                        per element of the projection), before the rotation
+                        per element of the projection), before the rotation; with "per_head": True every head is
+                        divided by the root mean square of its OWN elements instead, and the two weights hold
+                        ``head_dim`` numbers that all heads share
+  ``output_gate``       {"name", "kind"}: a matrix [heads x v_head_dim, H] named ``name`` under the prefix, held as further
+                        rows of the fused input matrix; the heads side by side are multiplied element by element by
+                        sigmoid ("sigmoid") or SiLU ("silu") of that projection of the mixer's input before the output
+                        product
+  ``output_scale``      a factor on the mixer's result (applied to the rows that enter the output product)
   ``chunk``             instead of a window: positions are counted off in chunks of that many from 0, and a token
                         sees the keys of its own chunk up to itself
   ``fp32_weights``      the softmax's weights and the weighted sum of values stay in 32-bit (the general kernel)
@@ -64,7 +71,7 @@ class GroupedQueryAttention(Mixer):
                  query_temperature: Optional[tuple] = None, tensor_names: Optional[dict] = None,
                  bias_names: Optional[dict] = None, sink_name: Optional[str] = None,
                  values_from_keys: bool = False, qk_norm: Optional[dict] = None, chunk: Optional[int] = None,
-                 fp32_weights: bool = False):
+                 fp32_weights: bool = False, output_gate: Optional[dict] = None, output_scale: float = 1.0):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
@@ -89,6 +96,15 @@ class GroupedQueryAttention(Mixer):
         self.qk_norm = None
         if qk_norm is not None:
             self.qk_norm = (float(qk_norm["eps"]), qk_norm.get("q", "q.norm"), qk_norm.get("k", "k.norm"))
+        self.qk_norm_per_head = bool(qk_norm and qk_norm.get("per_head", False))
+        if self.qk_norm_per_head and self.values_from_keys:
+            raise ValueError("a norm per head does not go with values taken from the keys")
+        self.output_gate = None
+        if output_gate is not None:
+            self.output_gate = (output_gate["name"], output_gate.get("kind", "sigmoid"))
+            if self.output_gate[1] not in ("sigmoid", "silu"):
+                raise ValueError(f"output gate '{self.output_gate[1]}' is not known (sigmoid, silu)")
+        self.output_scale = float(output_scale)
         self.q_norm_weight = self.k_norm_weight = None
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
@@ -102,6 +118,7 @@ class GroupedQueryAttention(Mixer):
             raise ValueError("a norm over the whole projection, a scaled rotation or values taken from the keys do not "
                              "go with unit-normed heads or a query temperature")
         self.plain = (self.v_head_dim == self.head_dim and self.qk_unit_norm_eps is None
+                      and self.output_gate is None and self.output_scale == 1.0
                       and self.query_temperature is None and sink_name is None and not self.rotary_prepare
                       and self.chunk is None and not self.fp32_weights
                       and not getattr(self.position, "learned_scores", False))
@@ -127,8 +144,11 @@ class GroupedQueryAttention(Mixer):
         if not self.values_from_keys:
             specs.append(TensorSpec(self._matrix_name(prefix, "v"), (self.v_size, H), "matrix"))
         if self.qk_norm is not None:
-            specs += [TensorSpec(f"{prefix}.{self.qk_norm[1]}", (Q,), "norm"),
-                      TensorSpec(f"{prefix}.{self.qk_norm[2]}", (KV,), "norm")]
+            nq, nk = (self.head_dim, self.head_dim) if self.qk_norm_per_head else (Q, KV)
+            specs += [TensorSpec(f"{prefix}.{self.qk_norm[1]}", (nq,), "norm"),
+                      TensorSpec(f"{prefix}.{self.qk_norm[2]}", (nk,), "norm")]
+        if self.output_gate is not None:
+            specs.append(TensorSpec(f"{prefix}.{self.output_gate[0]}", (self.o_size, H), "matrix"))
         if self.bias_names:
             specs += [TensorSpec(f"{prefix}.{self.bias_names[n]}", (size,), "bias")
                       for n, size in zip(self._inputs, (Q, KV, self.v_size))]
@@ -150,6 +170,8 @@ class GroupedQueryAttention(Mixer):
 
     def bind(self, tensors, prefix):
         w = [tensors.pop(self._matrix_name(prefix, n)) for n in self._inputs]
+        if self.output_gate is not None:  # the gate's projection rides in the same product
+            w.append(tensors.pop(f"{prefix}.{self.output_gate[0]}"))
         self.qkv_weight = torch.cat(w, dim=0).contiguous()
         if self.bias_names:
             biases = [tensors.pop(f"{prefix}.{self.bias_names[n]}") for n in self._inputs]
@@ -163,6 +185,8 @@ class GroupedQueryAttention(Mixer):
             self.sink = tensors[f"{prefix}.{self.sink_name}"]
         if any(b is not None for b in biases):
             sizes = (self.q_size, self.kv_size, self.v_size)[:len(biases)]
+            if self.output_gate is not None:
+                biases, sizes = biases + [None], sizes + (self.o_size,)
             parts = [
                 b if b is not None else torch.zeros(n, dtype=torch.float32, device=self.qkv_weight.device)
                 for b, n in zip(biases, sizes)
@@ -182,16 +206,21 @@ class GroupedQueryAttention(Mixer):
         T = x.shape[0]
         nh, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         meta = ctx.paged[cache.group]
-        qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + self.kv_size + self.v_size), x.dtype)
+        n_qkv = self.q_size + self.kv_size + self.v_size
+        qkv = ctx.workspace.get("attn_qkv", (T, self.qkv_weight.shape[0]), x.dtype)
         if not self.plain:
             dv = self.v_head_dim
             ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
+            gate = None
+            if self.output_gate is not None:
+                qkv, gate = qkv[:, :n_qkv], qkv[:, n_qkv:]
             if self.rotary_prepare:
                 rotary = self.position.table(qkv.device) if hasattr(self.position, "table") else None
                 ops.qk_norm_rotary_cache_write(qkv, ctx, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
                                                self.q_norm_weight, self.k_norm_weight,
                                                self.qk_norm[0] if self.qk_norm else 0.0, rotary,
-                                               values_from_keys=self.values_from_keys, write_kv=owns_cache)
+                                               values_from_keys=self.values_from_keys, write_kv=owns_cache,
+                                               per_head=self.qk_norm_per_head)
             else:
                 ops.qk_prepare_cache_write(qkv, ctx.positions, meta.slot_mapping, cache.k, cache.v, nh, nkv, d, dv,
                                            self.qk_unit_norm_eps, self.query_temperature, write_kv=owns_cache)
@@ -202,6 +231,10 @@ class GroupedQueryAttention(Mixer):
             ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d, self.window or 0,
                                 self.scale, score_slopes=terms, v_head_dim=dv, chunk=self.chunk or 0,
                                 fp32_weights=self.fp32_weights)
+            if gate is not None:
+                ops.gate_mul(out, gate, out, self.output_gate[1], self.output_scale)
+            elif self.output_scale != 1.0:
+                raise NotImplementedError("a factor on the attention's result goes with an output gate")
             ops.gemm(out, self.o_weight, None, h, accumulate=accumulate)
             return
         table = self.position.rotary_table(qkv.device)

@@ -75,14 +75,15 @@ class ScaledSinusoidalEmbedding(Part):
 class OutputHead(Part):
     """``tied_to``: tensor name of the embedding table to use as the output matrix, or None
     when the folder has a matrix of its own under ``prefix``.  ``softcap``: the logits z become
-    softcap * tanh(z / softcap) (None: they stay as they are)."""
+    softcap * tanh(z / softcap) (None: they stay as they are).  ``logit_scale``: a factor on the logits (before a cap)."""
 
     def __init__(self, vocab_size: int, hidden_size: int, tied_to=None, weight_name: str = "weight",
-                 softcap: float = None):
+                 softcap: float = None, logit_scale: float = 1.0):
         self.vocab_size, self.hidden_size, self.tied_to = int(vocab_size), int(hidden_size), tied_to
         self.softcap = None if not softcap else float(softcap)
         if self.softcap is not None and not (self.softcap > 0.0):
             raise ValueError(f"a soft cap of {softcap}: a positive number is needed")
+        self.logit_scale = float(logit_scale)
         self.weight_name = weight_name  # "" = the tensor is named by the prefix itself
         self.weight = None
 
@@ -100,6 +101,8 @@ class OutputHead(Part):
     def forward(self, y, logits):
         """logits fp32 [n, V] = y [n, H] W^T."""
         ops.gemm(y, self.weight, None, logits)
+        if self.logit_scale != 1.0:
+            ops.scale_(logits, self.logit_scale)
         if self.softcap is not None:
             ops.softcap_(logits, self.softcap)
 
@@ -107,8 +110,9 @@ class OutputHead(Part):
         """tokens int32 [n] = the index of each row's greatest logit (the lowest among equals), probs fp32 [n] its
         softmax probability; the logits themselves are stored nowhere where a kernel can avoid it (the reference's
         fused product + argmax: crates/ferrisinfer-kernel/src/cpu/matmul.rs:190-274)."""
-        if self.softcap is not None:
-            # the cap keeps the order of the logits but changes the probabilities: logits, cap, then the greedy rows
+        if self.softcap is not None or self.logit_scale != 1.0:
+            # a cap or a factor changes the probabilities (a negative factor also the order): logits, factor, cap, then
+            # the greedy rows
             logits = workspace.get("logits", (y.shape[0], self.vocab_size), torch.float32)
             self.forward(y, logits)
             ops.sample(logits, tokens, probs)

@@ -8,9 +8,13 @@
 
 ``GroupedRMSNorm``: the row in ``groups`` equal consecutive parts, each divided by its own root mean square; the
 weight spans the whole row.  The tensor is named by ``weight_name`` under the part's prefix ("" = the prefix itself).
+``unit_offset``: the folder stores the weight around zero and the norm multiplies by 1 + w; the sum is formed once, in
+fp32, when the tensor arrives, so every kernel sees a plain weight.
 """
 
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from .base import Norm, TensorSpec
@@ -37,8 +41,10 @@ class RMSNorm(Norm):
 
 
 class GroupedRMSNorm(Norm):
-    def __init__(self, hidden_size: int, eps: float, groups: int = 1, weight_name: str = "weight"):
+    def __init__(self, hidden_size: int, eps: float, groups: int = 1, weight_name: str = "weight",
+                 unit_offset: bool = False):
         self.hidden_size, self.eps, self.groups = int(hidden_size), float(eps), int(groups)
+        self.unit_offset = bool(unit_offset)
         if self.groups < 1 or self.hidden_size % self.groups:
             raise ValueError(f"{self.hidden_size} columns cannot be normed in {self.groups} equal groups")
         self.weight_name = weight_name
@@ -48,10 +54,13 @@ class GroupedRMSNorm(Norm):
         return f"{prefix}.{self.weight_name}" if self.weight_name else prefix
 
     def tensor_specs(self, prefix):
-        return [TensorSpec(self._name(prefix), (self.hidden_size,), "norm")]
+        # a weight stored around zero is drawn like a bias in random folders
+        return [TensorSpec(self._name(prefix), (self.hidden_size,), "bias" if self.unit_offset else "norm")]
 
     def bind(self, tensors, prefix):
         self.weight = tensors[self._name(prefix)]
+        if self.unit_offset:
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
 
     def forward(self, h, out, row_index=None):
         ops.grouped_rmsnorm(h, self.weight, self.eps, self.groups, out, row_index)
@@ -66,7 +75,7 @@ class GroupedRMSNorm(Norm):
         """This norm and ``other`` of the same rows in one launch; False (nothing done) if ``other`` is not the same
         norm with another weight."""
         if not isinstance(other, GroupedRMSNorm) or (other.hidden_size, other.eps, other.groups) != (
-                self.hidden_size, self.eps, self.groups):
+                self.hidden_size, self.eps, self.groups):  # (either may store its weight around zero: both hold 1 + w)
             return False
         ops.grouped_rmsnorm_pair(h, self.weight, other.weight, self.eps, self.groups, out, other_out)
         return True

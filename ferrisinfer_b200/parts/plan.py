@@ -35,7 +35,9 @@ class TensorSpec:
     ``matrix`` / ``embedding``: the engine's compute dtype, N(0, 0.02);
     ``bias``: N(0, 0.02); ``norm``: 1 + N(0, 0.02); vectors (bias, norm) are
     held in 32-bit on the device (an exact widening of what the file stores);
-    ``int_table``: int32, zeros.
+    ``int_table``: int32, zeros.  A negative size in ``shape`` is one that the folder decides (a size that no
+    configuration key states): any size fits, the part reads it from the tensor it is given, and a random folder
+    draws its absolute value.
     """
 
     name: str

@@ -13,7 +13,18 @@
     S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
   h += (rmsnorm_in_groups(o * SiLU(z)) * n) Wo^T       the gate before the norm, ``norm_groups`` equal parts.
 
-Both hold all input matrices as one, so that one product feeds the convolution, the gates and the recurrence; the
+``GatedLinearUnit`` (the recurrent block of a Griffin-style model, with a real-gated linear recurrent unit):
+  b = a(y Wy^T + by), a the tanh form of GELU;  u = conv(y Wx^T + bx) + cb, a short causal convolution per channel, no
+  activation;  per block n of the C channels (C / blocks neighbours): r = sigmoid(Ra[n] u_n + ra), i = sigmoid(Ri[n] u_n + ri);
+    log a = -decay_factor r softplus(lam);  s_t = exp(log a) s_(t-1) + sqrt(1 - exp(2 log a)) i u_t
+  h += (s_t * b) Wo^T.   State: s [C] fp32 and the convolution's last taps - 1 inputs.
+
+``GatedLinearAttention`` (linear attention with a decay per key channel that the token sets):
+  q = y Wq^T dim^(-1/2), k = y Wk^T, v = y Wv^T;  alpha = sigmoid((y Wa1^T) Wa2^T + ba2)^(1 / tau), heads x dim;
+    S_t = diag(alpha_t) S_(t-1) + k_t v_t^T;  o_t = S_t^T q_t         per head
+  h += scale (rmsnorm_per_head(o) * n * SiLU(y Wg^T)) Wo^T,   n of size vdim, shared by the heads.
+
+All hold their input matrices as one, so that one product feeds the convolution, the gates and the recurrence; the
 state (S transposed, [heads, vdim, dim] fp32) and the convolution's last taps - 1 inputs are carried in the request's slot, so a
 sequence may be cut anywhere.  Decays, step sizes, unit norms, the recurrence and the norms are fp32 whatever the
 activations' type.
@@ -174,5 +185,153 @@ class StateSpaceDuality(Mixer):
         ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
 
 
+class GatedLinearUnit(Mixer):
+    accepts_lazy_norm = True
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size: int, width: int, blocks: int, conv_taps: int, decay_factor: float = 8.0,
+                 activation: str = "gelu_tanh", tensor_names: dict = None):
+        if width <= 0 or blocks <= 0 or width % blocks:
+            raise ValueError(f"{width} channels cannot stand in {blocks} equal blocks")
+        if conv_taps < 1:
+            raise ValueError(f"a convolution of {conv_taps} taps")
+        if activation not in ("gelu_tanh", "none"):
+            raise ValueError(f"activation '{activation}' of the gate branch is not known (gelu_tanh, none)")
+        self.hidden_size, self.width, self.blocks, self.taps = int(hidden_size), int(width), int(blocks), int(conv_taps)
+        self.decay_factor, self.activation = float(decay_factor), activation
+        self.names = {"y": "y", "x": "x", "conv": "conv", "ra": "ra", "ri": "ri", "lam": "lam", "o": "o"}
+        self.names.update(tensor_names or {})
+
+    def tensor_specs(self, prefix):
+        H, C, n, bs = self.hidden_size, self.width, self.names, self.width // self.blocks
+        return [
+            TensorSpec(f"{prefix}.{n['y']}", (C, H), "matrix"), TensorSpec(f"{prefix}.{n['y']}.b", (C,), "bias"),
+            TensorSpec(f"{prefix}.{n['x']}", (C, H), "matrix"), TensorSpec(f"{prefix}.{n['x']}.b", (C,), "bias"),
+            TensorSpec(f"{prefix}.{n['conv']}", (C, self.taps), "vector"), TensorSpec(f"{prefix}.{n['conv']}.b", (C,), "bias"),
+            TensorSpec(f"{prefix}.{n['ra']}", (self.blocks, bs, bs), "matrix"),
+            TensorSpec(f"{prefix}.{n['ra']}.b", (self.blocks, bs), "bias"),
+            TensorSpec(f"{prefix}.{n['ri']}", (self.blocks, bs, bs), "matrix"),
+            TensorSpec(f"{prefix}.{n['ri']}.b", (self.blocks, bs), "bias"),
+            TensorSpec(f"{prefix}.{n['lam']}", (C,), "vector"),
+            TensorSpec(f"{prefix}.{n['o']}", (H, C), "matrix"),
+        ]
+
+    def bind(self, tensors, prefix):
+        n = self.names
+        # one product: [gate branch | recurrent branch]
+        self.in_weight = _fused_rows([tensors.pop(f"{prefix}.{n['y']}"), tensors.pop(f"{prefix}.{n['x']}")])
+        bias = torch.cat([tensors[f"{prefix}.{n['y']}.b"], tensors[f"{prefix}.{n['x']}.b"]])
+        pad = self.in_weight.shape[0] - bias.numel()
+        self.in_bias = torch.cat([bias, bias.new_zeros(pad)]).contiguous() if pad else bias.contiguous()
+        self.conv_weight, self.conv_bias = tensors[f"{prefix}.{n['conv']}"], tensors[f"{prefix}.{n['conv']}.b"]
+        # the gates' matrices transposed ([block, in, out]): the threads of the gates kernel read consecutive weights
+        self.ra_t = tensors.pop(f"{prefix}.{n['ra']}").transpose(1, 2).contiguous()
+        self.ri_t = tensors.pop(f"{prefix}.{n['ri']}").transpose(1, 2).contiguous()
+        self.ra_bias = tensors[f"{prefix}.{n['ra']}.b"].reshape(-1).contiguous()
+        self.ri_bias = tensors[f"{prefix}.{n['ri']}.b"].reshape(-1).contiguous()
+        # softplus of the decay's parameter, formed once in 64-bit and rounded once
+        lam = tensors[f"{prefix}.{n['lam']}"]
+        self.rate = torch.nn.functional.softplus(lam.to(torch.float64)).to(torch.float32).contiguous()
+        self.o_weight = tensors[f"{prefix}.{n['o']}"]
+
+    def cache_need(self):
+        history = FixedState((self.taps - 1, self.width), torch.float32) if self.taps > 1 else None
+        return CombinedNeed((history, FixedState((self.width,), torch.float32)))
+
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
+        T, C = x.shape[0], self.width
+        history, state = cache.parts
+        ws = ctx.workspace
+        proj = ws.get("recurrent_in", (T, self.in_weight.shape[0]), ctx.act_dtype)
+        ops.gemm(x, self.in_weight, self.in_bias, proj)
+        u = ws.get("recurrent_conv", (T, C), ctx.act_dtype)
+        ops.short_conv(proj[:, C:2 * C], u, self.conv_weight, None if history is None else history.state, ctx,
+                       advance=owns_cache, bias=self.conv_bias, residual=False, silu=False)
+        a, b = ws.get("recurrent_unit_a", (T, C), torch.float32), ws.get("recurrent_unit_b", (T, C), torch.float32)
+        ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, a, b, self.decay_factor)
+        y = ws.get("recurrent_gated", (T, C), ctx.act_dtype)
+        ops.rglru_scan(a, b, proj[:, :C], y, state.state, ctx, gelu=self.activation == "gelu_tanh", write_state=owns_cache)
+        ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
+
+
+class GatedLinearAttention(Mixer):
+    accepts_lazy_norm = True
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, tau: float, norm_eps: float,
+                 decay_rank: int = None, output_scale: float = 1.0, tensor_names: dict = None):
+        """``decay_rank``: inner size of the decay's low-rank projection; None = whatever the folder's tensors have (a
+        random folder then draws 16)."""
+        if head_dim > 256:
+            raise ValueError(f"heads of {head_dim} are larger than the recurrence kernel takes (256)")
+        if not (tau > 0.0):
+            raise ValueError(f"a decay root of {tau}: a positive number is needed")
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.decay_rank = None if decay_rank is None else int(decay_rank)
+        self.tau, self.norm_eps, self.output_scale = float(tau), float(norm_eps), float(output_scale)
+        self.qk_size, self.v_size = self.num_heads * self.head_dim, self.num_heads * self.v_head_dim
+        self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2"}
+        self.names.update(tensor_names or {})
+
+    def tensor_specs(self, prefix):
+        H, n = self.hidden_size, self.names
+        rank = -16 if self.decay_rank is None else self.decay_rank  # negative: the folder decides
+        return [
+            TensorSpec(f"{prefix}.{n['q']}", (self.qk_size, H), "matrix"),
+            TensorSpec(f"{prefix}.{n['k']}", (self.qk_size, H), "matrix"),
+            TensorSpec(f"{prefix}.{n['v']}", (self.v_size, H), "matrix"),
+            TensorSpec(f"{prefix}.{n['g']}", (self.v_size, H), "matrix"),
+            TensorSpec(f"{prefix}.{n['o']}", (H, self.v_size), "matrix"),
+            TensorSpec(f"{prefix}.{n['norm']}", (self.v_head_dim,), "norm"),
+            TensorSpec(f"{prefix}.{n['a1']}", (rank, H), "matrix"),
+            TensorSpec(f"{prefix}.{n['a2']}", (self.qk_size, rank), "matrix"),
+            TensorSpec(f"{prefix}.{n['a2']}.b", (self.qk_size,), "bias"),
+        ]
+
+    def bind(self, tensors, prefix):
+        n = self.names
+        # one product: [q | k | v | gate | the decay's low-rank input], every part starting on a multiple of eight columns
+        a1, a2 = tensors.pop(f"{prefix}.{n['a1']}"), tensors.pop(f"{prefix}.{n['a2']}")
+        if a1.shape[0] != a2.shape[1]:
+            raise ValueError(f"{prefix}: the decay's two matrices do not meet ({tuple(a1.shape)} and {tuple(a2.shape)})")
+        self.decay_rank = int(a1.shape[0])
+        self.rank_cols = (self.decay_rank + 7) // 8 * 8
+        if self.rank_cols != self.decay_rank:
+            a1 = torch.cat([a1, a1.new_zeros(self.rank_cols - self.decay_rank, a1.shape[1])], dim=0)
+        self.in_weight = _fused_rows([tensors.pop(f"{prefix}.{n[w]}") for w in "qkvg"] + [a1])
+        self.a_off = 2 * self.qk_size + 2 * self.v_size
+        if self.rank_cols != self.decay_rank:  # zero columns meet the zero rows that fill the input matrix up
+            a2 = torch.cat([a2, a2.new_zeros(a2.shape[0], self.rank_cols - self.decay_rank)], dim=1)
+        self.a2_weight, self.a2_bias = a2.contiguous(), tensors[f"{prefix}.{n['a2']}.b"]
+        # the factor on the mixer's result rides in the norm's weight (fp32)
+        self.norm_weight = (tensors[f"{prefix}.{n['norm']}"].to(torch.float32) * self.output_scale).contiguous()
+        self.o_weight = tensors[f"{prefix}.{n['o']}"]
+
+    def cache_need(self):
+        # transposed: a column of S (one value dim) is a row of the slot
+        return FixedState((self.num_heads, self.v_head_dim, self.head_dim), torch.float32)
+
+    def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
+        T = x.shape[0]
+        nh, d, dv, QK, V = self.num_heads, self.head_dim, self.v_head_dim, self.qk_size, self.v_size
+        ws = ctx.workspace
+        proj = ws.get("linear_attn_in", (T, self.in_weight.shape[0]), ctx.act_dtype)
+        ops.gemm(x, self.in_weight, None, proj)
+        z = ws.get("linear_attn_decay", (T, QK), torch.float32)
+        ops.gemm(proj[:, self.a_off:self.a_off + self.rank_cols], self.a2_weight, self.a2_bias, z)
+        o = ws.get("linear_attn_out", (T, V), torch.float32)
+        ops.row_decay_recurrence(proj[:, :QK], proj[:, QK:2 * QK], proj[:, 2 * QK:2 * QK + V], z, 1.0 / self.tau, o,
+                                 cache.state, ctx, nh, d, dv, q_scale=d ** -0.5, write_state=owns_cache)
+        y = ws.get("linear_attn_gated", (T, V), ctx.act_dtype)
+        ops.gated_group_norm(o, proj[:, 2 * QK + V:2 * QK + 2 * V], self.norm_weight, self.norm_eps, y, group=dv,
+                             gate_kind="silu")
+        ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
+
+
+register_part("mixer", "gated_linear_unit", GatedLinearUnit)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)
 register_part("mixer", "state_space_duality", StateSpaceDuality)

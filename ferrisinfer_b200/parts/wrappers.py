@@ -6,7 +6,10 @@ is its state (a slot of [H], fp32, zero at admission), beside whatever the wrapp
 ``weight_name`` under the part's prefix and the wrapped mixer's tensors live under ``inner_prefix`` there.
 
 ``ParallelMixers``: every branch reads the same input; h += coef * sum_b rmsnorm(branch_b(y)) * w_b, the norm over the
-model width with a plain weight per branch (``<prefix>.<name>.out``); coef is 1 / branches unless given.
+model width with a plain weight per branch (``<prefix>.<name>.out``); coef is 1 / branches unless given.  With
+``norm=False`` the branches' results are simply added, h += sum_b branch_b(y): every branch then adds into the residual
+rows itself (a factor on a branch's result is that branch's own parameter), and there are no tensors beside the
+branches'.
 """
 
 from __future__ import annotations
@@ -71,7 +74,8 @@ class ParallelMixers(Mixer):
     accepts_lazy_norm = False
     can_overwrite = True
 
-    def __init__(self, hidden_size: int, branches: dict, norm_eps: float, coef: float = None, out_name: str = "out"):
+    def __init__(self, hidden_size: int, branches: dict, norm_eps: float = 0.0, coef: float = None, out_name: str = "out",
+                 norm: bool = True):
         """``branches``: name -> PartSpec of a mixer (one to four), in order."""
         if not 1 <= len(branches) <= 4:
             raise ValueError(f"{len(branches)} mixers side by side (one to four)")
@@ -79,7 +83,9 @@ class ParallelMixers(Mixer):
         self.names = list(branches)
         self.mixers = [build_part("mixer", b) if isinstance(b, PartSpec) else b for b in branches.values()]
         self.coef = 1.0 / len(self.mixers) if coef is None else float(coef)
-        self.out_name = out_name
+        self.out_name, self.norm = out_name, bool(norm)
+        if not self.norm and coef is not None:
+            raise ValueError("branches that are simply added take their factors themselves")
         self.out_weights = None
 
     @property
@@ -90,17 +96,30 @@ class ParallelMixers(Mixer):
         specs = []
         for name, m in zip(self.names, self.mixers):
             specs += m.tensor_specs(f"{prefix}.{name}")
+        if not self.norm:
+            return specs
         return specs + [TensorSpec(f"{prefix}.{name}.{self.out_name}", (self.hidden_size,), "norm") for name in self.names]
 
     def bind(self, tensors, prefix):
         for name, m in zip(self.names, self.mixers):
             m.bind(tensors, f"{prefix}.{name}")
+        if not self.norm:
+            return
         self.out_weights = [tensors[f"{prefix}.{name}.{self.out_name}"] for name in self.names]
 
     def cache_need(self):
         return CombinedNeed(tuple(m.cache_need() for m in self.mixers))
 
     def forward(self, x, h, ctx, cache: LayerCache, owns_cache: bool, accumulate: bool = True):
+        if not self.norm:  # every branch adds into h; the first replaces it where the caller wants the result alone
+            for i, m in enumerate(self.mixers):
+                if i == 0 and not accumulate:
+                    if getattr(m, "can_overwrite", False):
+                        m.forward(x, h, ctx, cache.parts[i], owns_cache, accumulate=False)
+                        continue
+                    h.zero_()
+                m.forward(x, h, ctx, cache.parts[i], owns_cache)
+            return
         T = x.shape[0]
         results = ctx.workspace.get("parallel_mixers_out", (len(self.mixers), T, self.hidden_size), torch.float32)
         for i, m in enumerate(self.mixers):

@@ -46,6 +46,13 @@ def parse_dtype(dtype) -> torch.dtype:
         raise ValueError(f"compute dtype must be bfloat16 or float32, found {dtype!r}") from None
 
 
+def shape_fits(wanted, found) -> bool:
+    """Whether a tensor of shape ``found`` is what a spec of shape ``wanted`` asks for; a negative size in ``wanted``
+    is one that the folder decides (a part then reads it from the tensor it is given)."""
+    wanted, found = tuple(wanted), tuple(found)
+    return len(wanted) == len(found) and all(w < 0 or w == f for w, f in zip(wanted, found))
+
+
 def check_tensors(specs, found: dict, ignorable=(), where: str = "", strict: bool = True) -> list:
     """``found``: name -> shape of what the folder (or dict) holds.  Raises ONE WeightLoadError that lists every
     missing tensor, every unexpected tensor and every wrong shape.  ``strict`` False: tensors that the model
@@ -55,7 +62,7 @@ def check_tensors(specs, found: dict, ignorable=(), where: str = "", strict: boo
     missing = [s.name for s in specs if s.required and s.name not in found]
     unexpected = [n for n in found if n not in wanted and n not in ignorable]
     wrong = [
-        (n, wanted[n].shape, tuple(found[n])) for n in found if n in wanted and tuple(found[n]) != tuple(wanted[n].shape)
+        (n, wanted[n].shape, tuple(found[n])) for n in found if n in wanted and not shape_fits(wanted[n].shape, found[n])
     ]
     if missing or wrong or (unexpected and strict):
         raise WeightLoadError(sorted(missing), sorted(unexpected), sorted(wrong), where)

@@ -35,7 +35,8 @@ def random_tensor(spec, seed: int, store_dtype: torch.dtype, device="cpu"):
     if spec.role == "int_table":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     g = _generator(seed, spec.name, device)
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * INIT_STD
+    shape = tuple(abs(n) for n in spec.shape)  # a size that the folder decides: -n draws n
+    t = torch.randn(shape, generator=g, dtype=torch.float32, device=device) * INIT_STD
     if spec.role == "norm":
         t = t + 1.0
     return t.to(store_dtype)
