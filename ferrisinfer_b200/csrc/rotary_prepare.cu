@@ -206,13 +206,16 @@ __global__ void __launch_bounds__(256) qk_norm_rotary_cache_write_paired_kernel(
 // The norm per HEAD: every q and k head divided by the root mean square of its own d elements and multiplied by a
 // weight of d numbers that all heads share (wq for queries, wk for keys; null: that side is not normed), then rotated
 // and stored as above.  A warp per head: its lanes sum the head's squares, then norm, rotate and store it; the values
-// are copied by the whole block.
+// are copied by the whole block.  With freq_lo (what the 32-bit frequencies lack of their 64-bit values) the angle
+// position x frequency keeps the digits that one 32-bit product rounds away: the product's own rounding error comes
+// from an FMA, the frequency's from freq_lo, and the small sum e of the two enters as sin(a + e) = sin a + e cos a,
+// cos(a + e) = cos a - e sin a.  At position 1,000 a 32-bit angle is off by up to 6e-5 rad, which shows in 32-bit logits.
 template <typename T>
 __global__ void __launch_bounds__(256) qk_head_norm_rotary_cache_write_kernel(
     T* qkv, int ld, const int* __restrict__ positions, const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
     T* __restrict__ v_cache, int nh, int nkv, int d, int dv, int page_size, const float* __restrict__ q_weight,
     const float* __restrict__ k_weight, float eps, const float* __restrict__ freq, int rotary, int interleaved, float mag,
-    int write_kv) {
+    int write_kv, const float* __restrict__ freq_lo) {
     extern __shared__ float cs[];  // the token's cosines, then its sines, both times mag
     pdl_wait();
     pdl_launch_dependents();
@@ -220,8 +223,15 @@ __global__ void __launch_bounds__(256) qk_head_norm_rotary_cache_write_kernel(
     const int pos = positions[t];
     const int half = rotary >> 1;
     for (int f = threadIdx.x; f < half; f += blockDim.x) {
+        const float p = (float)pos, hi = freq[f];
+        const float angle = p * hi;
         float s, c;
-        sincosf((float)pos * freq[f], &s, &c);
+        sincosf(angle, &s, &c);
+        if (freq_lo) {
+            const float e = fmaf(p, hi, -angle) + p * freq_lo[f];
+            const float s0 = s;
+            s = fmaf(e, c, s), c = fmaf(-e, s0, c);
+        }
         cs[f] = c * mag, cs[half + f] = s * mag;
     }
     __syncthreads();
@@ -318,11 +328,13 @@ FERRIS_API int ferris_qk_norm_rotary_cache_write(void* qkv, int ld, int dtype, c
 }
 
 // As above with the norm taken per head: q_weight, k_weight fp32 [d] (shared by the heads; null: no norm on that side).
+// freq_lo (may be null): fp32 [rotary / 2], the 64-bit frequencies minus their 32-bit roundings.
 FERRIS_API int ferris_qk_head_norm_rotary_cache_write(void* qkv, int ld, int dtype, const int* positions,
                                                       const int* slot_mapping, void* k_cache, void* v_cache, int tokens,
                                                       int nh, int nkv, int d, int dv, int page_size, const float* q_weight,
                                                       const float* k_weight, float eps, const float* freq, int rotary,
-                                                      int interleaved, float mag, int write_kv, void* stream) {
+                                                      int interleaved, float mag, int write_kv, const float* freq_lo,
+                                                      void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (nh <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0)
         FERRIS_REFUSE("head norm + rotation: nh=%d nkv=%d d=%d dv=%d page_size=%d", nh, nkv, d, dv, page_size);
@@ -336,11 +348,11 @@ FERRIS_API int ferris_qk_head_norm_rotary_cache_write(void* qkv, int ld, int dty
     if (dtype == FERRIS_F32)
         ferris_launch(qk_head_norm_rotary_cache_write_kernel<float>, dim3(tokens), dim3(threads), smem, s, (float*)qkv, ld,
                       positions, slot_mapping, (float*)k_cache, (float*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight,
-                      eps, freq, rotary, interleaved, mag, write_kv);
+                      eps, freq, rotary, interleaved, mag, write_kv, freq_lo);
     else if (dtype == FERRIS_BF16)
         ferris_launch(qk_head_norm_rotary_cache_write_kernel<bf16>, dim3(tokens), dim3(threads), smem, s, (bf16*)qkv, ld,
                       positions, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, d, dv, page_size, q_weight, k_weight, eps,
-                      freq, rotary, interleaved, mag, write_kv);
+                      freq, rotary, interleaved, mag, write_kv, freq_lo);
     else
         FERRIS_REFUSE("head norm + rotation: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();

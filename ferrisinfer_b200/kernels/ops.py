@@ -1428,13 +1428,16 @@ def head_gemm(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.T
 class RotaryTable:
     """A rotation of the first ``rotary_dim`` elements of a head by position x frequency: ``freq`` fp32 [rotary_dim / 2]
     on the device; ``interleaved``: the pairs are the elements (2i, 2i + 1), else (i, i + rotary_dim / 2);
-    ``magnitude``: a factor on every cosine and sine."""
+    ``magnitude``: a factor on every cosine and sine.  ``freq_lo`` (optional, fp32 like ``freq``): what ``freq`` lacks of
+    the frequencies' 64-bit values; a kernel that takes it forms position x frequency beyond 32-bit rounding."""
 
-    __slots__ = ("freq", "rotary_dim", "interleaved", "magnitude")
+    __slots__ = ("freq", "rotary_dim", "interleaved", "magnitude", "freq_lo")
 
-    def __init__(self, freq: torch.Tensor, rotary_dim: int, interleaved: bool = False, magnitude: float = 1.0):
+    def __init__(self, freq: torch.Tensor, rotary_dim: int, interleaved: bool = False, magnitude: float = 1.0,
+                 freq_lo: Optional[torch.Tensor] = None):
         self.freq, self.rotary_dim = freq, int(rotary_dim)
         self.interleaved, self.magnitude = bool(interleaved), float(magnitude)
+        self.freq_lo = freq_lo
 
 
 def _rotary_args(rotary: Optional[RotaryTable], ctx, head_dim: int, device) -> tuple:
@@ -1519,7 +1522,8 @@ def qk_norm_rotary_cache_write(qkv: torch.Tensor, ctx, slot_mapping: Optional[to
                 _ptr(qkv), _c_int(ld), _c_int(_dt(qkv, "qkv")), _ptr(ctx.positions), _ptr(slot_mapping if write_kv else None),
                 _ptr(k_cache if write_kv else None), _ptr(v_cache if write_kv else None), _c_int(T), _c_int(num_heads),
                 _c_int(num_kv_heads), _c_int(head_dim), _c_int(v_head_dim), _c_int(page_size), _ptr(q_norm), _ptr(k_norm),
-                _c_float(eps), freq, rdim, inter, mag, _c_int(1 if write_kv else 0), _stream()),
+                _c_float(eps), freq, rdim, inter, mag, _c_int(1 if write_kv else 0),
+                _ptr(rotary.freq_lo if rotary is not None and rotary.rotary_dim else None), _stream()),
             "head norm + rotation + cache write",
         )
         return

@@ -105,7 +105,10 @@ class ScaledRotary(PositionEncoding):
                 ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
                 freq[i] = f / factor * ramp + f * (1.0 - ramp)
             self.magnitude = 0.1 * math.log(factor) + 1.0
-        self._host = np.asarray(freq, dtype=np.float64).astype(np.float32)
+        exact = np.asarray(freq, dtype=np.float64)
+        self._host = exact.astype(np.float32)
+        # what the 32-bit frequencies lack of the 64-bit ones, for kernels that form their angles beyond 32-bit rounding
+        self._host_lo = (exact - self._host.astype(np.float64)).astype(np.float32)
         self._device = {}
 
     def rotary_table(self, device=None):
@@ -117,7 +120,8 @@ class ScaledRotary(PositionEncoding):
         key = str(device)
         if key not in self._device:
             self._device[key] = ops.RotaryTable(torch.from_numpy(self._host.copy()).to(device), self.rotary_dim,
-                                                self.layout == "interleaved", self.magnitude)
+                                                self.layout == "interleaved", self.magnitude,
+                                                freq_lo=torch.from_numpy(self._host_lo.copy()).to(device))
         return self._device[key]
 
 

@@ -225,4 +225,4 @@ def forward(cfg, w, ids, start=0, state=None, dtype=torch.float64, after_layer=N
         if after_layer is not None:
             after_layer(i, x)
     y = norm_one_plus(x, w["final.norm"], eps)
-    return (y @ w["embed"].T) * float(cfg["logit_scale"]), state
+    return (y @ w["embed"].T) * float(cfg.get("logit_scale", 1.0)), state
