@@ -556,9 +556,10 @@ def main() -> int:
                     help="instead of the measurement: the Kugilix decoder beside the Qwen2 decoder at equal layer sizes "
                          "(names of bench_designs.SIZES, with commas): prefill and decode through the step function, and "
                          "the Kugilix design's own kernels alone; prints one JSON line of its own")
-    ap.add_argument("--design", default="kugilix", choices=["kugilix", "nusudra", "netinex"],
+    ap.add_argument("--design", default="kugilix", choices=["kugilix", "nusudra", "netinex", "sumevik"],
                     help="with --designs: which design is set beside the others (kugilix: beside Qwen2; nusudra or "
-                         "netinex: beside Kugilix and Qwen2, with its own kernels alone as well)")
+                         "netinex: beside Kugilix and Qwen2, with its own kernels alone as well; sumevik: beside Netinex "
+                         "and Qwen2, with its own kernels and Netinex's alone)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

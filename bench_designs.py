@@ -1,7 +1,9 @@
 """Designs side by side at equal layer sizes: the Kugilix decoder beside the Qwen2 dense decoder, or (``design`` =
-"nusudra" / "netinex") the Nusudra or the Netinex decoder beside both, random weights.
+"nusudra" / "netinex") the Nusudra or the Netinex decoder beside both, or (``design`` = "sumevik") the Sumevik decoder
+beside the Netinex decoder (the closest existing design: attention within chunks, a linear recurrence, experts) and
+Qwen2, random weights.
 
-Called by ``bench.py --designs [--design nusudra|netinex]``.  For each of a few sizes that resemble a real model's layers it measures, through
+Called by ``bench.py --designs [--design nusudra|netinex|sumevik]``.  For each of a few sizes that resemble a real model's layers it measures, through
 the step function, the prefill of one prompt and decode steps at two batch sizes for both designs, and times the
 kernels that only the Kugilix design has (decayed linear attention, the windowed attention with slopes, the short
 convolution, the norms in groups, the gated norm, the activation) alone, with what they reach of the measured copy
@@ -105,6 +107,36 @@ def netinex_config(s: dict) -> dict:
     order = [att, ret, ret]
     return {"architecture": "Netinex", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
             "layers": [order[i % 3] for i in range(kugilix_runs(s))]}
+
+
+SUMEVIK_IDENTITY = 2  # router outputs beside the EXPERTS experts that stand for "the token's own row"
+
+
+def sumevik_dense_ff(s: dict) -> int:
+    """The inner size of a gated feed-forward of as many weights as the plain one of ``ff`` (three matrices for two)."""
+    return (2 * s["ff"] // 3 + 127) // 128 * 128
+
+
+def sumevik_config(s: dict) -> dict:
+    """As many layers as the Kugilix model has layer runs: two recurrent layers, then an attention beside a gated linear
+    attention, and so on; the recurrence as wide as the model with as many gate blocks as heads; the same heads and head
+    size, chunks as long as the other designs' window, half of every head rotating; the linear attention with as many
+    heads, keys of half and values of the full head size; a gated feed-forward in every second layer, ``TOP`` of
+    ``EXPERTS`` experts (+ ``SUMEVIK_IDENTITY`` identity experts, two groups of which one stays) in the others."""
+    H, G, d, W = s["heads"], s["kv_heads"], s["dim"], s["width"]
+    outputs = EXPERTS + SUMEVIK_IDENTITY
+    moe = {"kind": "moe", "expert": {"ff": netinex_expert_ff(s), "limit": 7.0},
+           "router": {"experts": EXPERTS, "identity": SUMEVIK_IDENTITY, "top": TOP, "groups": {"count": 2, "keep": 1}}}
+    assert outputs % 2 == 0
+    dense = {"kind": "dense", "ff": sumevik_dense_ff(s)}
+    rec = {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 1.0 / math.sqrt(d),
+                              "mask": {"size": WINDOW}, "rot": {"base": 1000000.0, "dims": d // 2}},
+                     "right": {"heads": H, "dim": d // 2, "vdim": d, "tau": 16.0}, "left_scale": 0.8, "right_scale": 1.1}}
+    order = [rec, rec, par]
+    layers = [dict(order[i % 3], mlp=moe if i % 2 else dense) for i in range(kugilix_runs(s))]
+    return {"architecture": "Sumevik", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "logit_scale": 0.5, "layers": layers}
 
 
 def _timed(fn, flush, warmup=3, iters=5, reps=1):
@@ -477,10 +509,162 @@ def netinex_kernel_numbers(s: dict, peaks: dict) -> dict:
     return out
 
 
+def sumevik_kernel_numbers(s: dict, peaks: dict) -> dict:
+    """The Sumevik design's own kernels alone at the layer sizes ``s``, measured as ``kernel_numbers`` measures; its gated
+    products beside the SiLU-gated ones, its router and experts beside the Netinex design's."""
+    import torch
+    from types import SimpleNamespace
+
+    from ferrisinfer_b200.engine.workspace import Workspace
+    from ferrisinfer_b200.kernels import ops
+
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.zeros(96 << 20, dtype=torch.float32, device=dev)  # 384 MB
+    W, H, G, d, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    hbm = peaks["hbm_gbs"] * 1e9
+    tensor = peaks["bf16_tflops"] * 1e12
+    ws = Workspace(dev)
+    out = {}
+
+    def ctx_of(q_lens, start):
+        S = len(q_lens)
+        q_start = [0]
+        for n in q_lens:
+            q_start.append(q_start[-1] + n)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        return SimpleNamespace(num_tokens=q_start[-1], num_seqs=S, max_q_len=max(q_lens), workspace=ws,
+                               max_kv_len=start + max(q_lens),
+                               token_seq=i32([i for i in range(S) for _ in range(q_lens[i])]),
+                               positions=i32([start + j for i in range(S) for j in range(q_lens[i])]),
+                               seq_q_start=i32(q_start), seq_start_pos=i32([start] * S), seq_state_slot=i32(list(range(S))))
+
+    def record(name, seconds, bytes_=None, flops=None, tensor_flops=None):
+        e = {"us": round(seconds * 1e6, 1)}
+        if bytes_ is not None:
+            e["GBps"] = round(bytes_ / seconds / 1e9, 1)
+            e["frac_hbm"] = round(bytes_ / seconds / hbm, 3)
+        if flops is not None:
+            e["TFLOPs_fp32"] = round(flops / seconds / 1e12, 2)
+            e["frac_fp32_nominal"] = round(flops / seconds / (FP32_NOMINAL_TFLOPS * 1e12), 3)
+        if tensor_flops is not None:
+            e["TFLOPs_bf16"] = round(tensor_flops / seconds / 1e12, 1)
+            e["frac_bf16_measured"] = round(tensor_flops / seconds / tensor, 3)
+        out[name] = e
+
+    # ---- the recurrent unit: gates (block-diagonal products, sigmoids, decay) and the scan over channels
+    C, blocks = W, H
+    bs = C // blocks
+    wa = (torch.randn(blocks, bs, bs, device=dev) / math.sqrt(bs)).to(bf)
+    wi = (torch.randn(blocks, bs, bs, device=dev) / math.sqrt(bs)).to(bf)
+    ba, bi, rate = torch.zeros(C, device=dev), torch.zeros(C, device=dev), torch.full((C,), 0.05, device=dev)
+    for tag, q_lens in (("decode_b64", [1] * 64), ("prefill_2048", [2048])):
+        T, S = sum(q_lens), len(q_lens)
+        reps = 10 if T <= 64 else 1
+        u = torch.randn(T, C, device=dev).to(bf)
+        ybranch = torch.randn(T, C, device=dev).to(bf)
+        a, b = torch.empty(T, C, device=dev), torch.empty(T, C, device=dev)
+        y = torch.empty(T, C, dtype=bf, device=dev)
+        state = torch.zeros(S + 1, C, device=dev)
+        ctx = ctx_of(q_lens, 5)
+        t = _timed(lambda: ops.rglru_gates(u, wa, wi, ba, bi, rate, a, b, 8.0), flush, reps=reps)
+        record(f"recurrent_gates_{tag}", t, bytes_=2 * C * bs * 2 + T * C * (2 + 8), flops=2.0 * T * 2 * C * bs)
+        t = _timed(lambda: ops.rglru_scan(a, b, ybranch, y, state, ctx), flush, reps=reps)
+        record(f"recurrent_scan_{tag}", t, bytes_=T * C * (8 + 2 + 2) + 2 * S * C * 4)
+        cw = torch.randn(C, 4, device=dev) * 0.1
+        cb = torch.zeros(C, device=dev)
+        hist = torch.zeros(S + 1, 3, C, device=dev)
+        wide = torch.randn(T, 2 * C, device=dev).to(bf)
+        t = _timed(lambda: ops.short_conv(wide[:, C:], u, cw, hist, ctx, bias=cb, residual=False), flush, reps=reps)
+        record(f"recurrent_conv_{tag}", t, bytes_=T * C * 4 + (S * 3 * C * 8 if T <= 64 else 0))
+    # ---- the gated linear attention: the recurrence with a decay per key channel, and the norm per head with its gate
+    dk = d // 2
+    for tag, q_lens in (("decode_b64", [1] * 64), ("prefill_2048", [2048])):
+        T, S = sum(q_lens), len(q_lens)
+        proj = (torch.randn(T, 2 * H * dk + 2 * H * d, device=dev) / 4.0).to(bf)
+        z = 3.0 + torch.randn(T, H * dk, device=dev)
+        state = torch.zeros(S + 1, H, d, dk, device=dev)
+        o = torch.empty(T, H * d, device=dev)
+        ctx = ctx_of(q_lens, 0)
+        t = _timed(lambda: ops.row_decay_recurrence(proj[:, :H * dk], proj[:, H * dk:2 * H * dk], proj[:, 2 * H * dk:2 * H * dk + H * d],
+                                                    z, 1.0 / 16.0, o, state, ctx, H, dk, d, q_scale=dk ** -0.5), flush)
+        moved = 2 * S * H * dk * d * 4 + T * (2 * H * dk + H * d) * 2 + T * H * dk * 4 + T * H * d * 4
+        record(f"linear_attention_row_decay_{tag}", t, bytes_=moved, flops=4.0 * T * H * dk * d)
+    # ---- the attention's own kernels: norm per head + rotation + cache write, the chunked attention with value heads of
+    # their own, the gate on its output
+    freq = torch.exp(-math.log(1e6) * torch.arange(d // 4, device=dev, dtype=torch.float32) * 4 / d)
+    itab = ops.RotaryTable(freq, d // 2, interleaved=True, freq_lo=torch.zeros_like(freq))
+    for name, batch, q_len, ctx_len in (("decode_b64", 64, 1, 2047), ("prefill_2048", 1, 2048, 0)):
+        T = batch * q_len
+        reps = 10 if T <= 64 else 1
+        pages_each = (ctx_len + q_len + 15) // 16
+        k = torch.randn(batch * pages_each + 1, G, 16, d, device=dev).to(bf)
+        v = torch.randn_like(k)
+        tables = torch.arange(batch * pages_each, dtype=torch.int32, device=dev).view(batch, pages_each)
+        rows = torch.randn(T, (H + 2 * G) * d + H * d, device=dev).to(bf)  # q, k, v and the gate's columns
+        qkv, gate = rows[:, :(H + 2 * G) * d], rows[:, (H + 2 * G) * d:]
+        o = torch.empty(T, H * d, dtype=bf, device=dev)
+        ctx = ctx_of([q_len] * batch, ctx_len)
+        slots = (tables[ctx.token_seq.long(), (ctx.positions // 16).long()] * 16 + ctx.positions % 16).int()
+        qn, kn = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        t = _timed(lambda: ops.qk_norm_rotary_cache_write(qkv, ctx, slots, k, v, H, G, d, d, qn, kn, 1e-6, itab, per_head=True),
+                   flush, reps=10)
+        record(f"head_norm_rotary_{name}", t, bytes_=T * (2 * H * d + 4 * G * d) * 2)
+        t = _timed(lambda: ops.paged_attention_simt(qkv, o, k, v, tables, ctx.token_seq, ctx.positions, H, G, d, 0,
+                                                    1.0 / math.sqrt(d), v_head_dim=d, max_q_len=q_len,
+                                                    max_kv_len=ctx_len + q_len, workspace=ws, chunk=WINDOW), flush)
+        keys = sum((ctx_len + j) % WINDOW + 1 for j in range(q_len)) * batch
+        record(f"chunk_attention_{name}", t, flops=4.0 * keys * H * d,
+               bytes_=batch * G * (ctx_len % WINDOW + 1) * 2 * d * 2 + T * H * d * 4 if q_len == 1 else None)
+        t = _timed(lambda: ops.gate_mul(o, gate, o, "sigmoid", 0.8), flush, reps=reps)
+        record(f"output_gate_{name}", t, bytes_=T * H * d * 6)
+        og = torch.randn(T, H * d, device=dev)
+        yy = torch.empty(T, H * d, dtype=bf, device=dev)
+        t = _timed(lambda: ops.gated_group_norm(og, gate, torch.ones(d, device=dev), 1e-6, yy, group=d, gate_kind="silu"), flush, reps=reps)
+        record(f"head_norm_silu_gate_{name}", t, bytes_=T * H * d * (4 + 2 + 2))
+    # ---- the gated feed-forward: the tanh GELU in the products' epilogues beside the SiLU of the other designs
+    inter = sumevik_dense_ff(s)
+    gate_up_w = (torch.randn(2 * inter, W, device=dev) / math.sqrt(W)).to(bf)
+    for tag, T in (("b8", 8), ("b64", 64), ("2048", 2048)):
+        x = torch.randn(T, W, device=dev).to(bf)
+        act = torch.empty(T, inter, dtype=bf, device=dev)
+        for kind in ("gelu_tanh", "silu"):
+            t = _timed(lambda: ops.gemm_gated(x, gate_up_w, act, kind, 0.0, ws), flush)
+            record(f"gated_product_{kind}_{tag}", t, bytes_=2 * inter * W * 2 + T * (W + inter) * 2,
+                   tensor_flops=2.0 * T * 2 * inter * W)
+    # ---- the scored router and the experts with a clamped gate and identity experts
+    eff = netinex_expert_ff(s)
+    outputs = EXPERTS + SUMEVIK_IDENTITY
+    gate_up = (torch.randn(EXPERTS, 2 * eff, W, device=dev) / math.sqrt(W)).to(bf)
+    down = (torch.randn(EXPERTS, W, eff, device=dev) / math.sqrt(eff)).to(bf)
+    router = torch.randn(outputs, W, device=dev).to(bf)
+    corr = torch.zeros(outputs, device=dev)
+    for tag, T in (("b8", 8), ("b64", 64), ("2048", 2048)):
+        x = torch.randn(T, W, device=dev).to(bf)
+        hrow = torch.zeros(T, W, device=dev)
+        ids = torch.empty(T, TOP, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, TOP, device=dev)
+        idw = torch.empty(T, device=dev)
+        scored = {"correction": corr, "groups": 2, "keep": 1, "with_weights": EXPERTS, "identity_w": idw}
+        t = _timed(lambda: ops.moe_router(x, router, None, ids, wts, TOP, scored=scored), flush, reps=10)
+        record(f"scored_router_{tag}", t, bytes_=T * W * 2 + outputs * W * 2)
+        chosen = torch.unique(ids)
+        distinct = int((chosen < EXPERTS).sum())
+        pairs = int((ids < EXPERTS).sum())
+        t = _timed(lambda: ops.moe_experts(x, gate_up, down, ids, wts, hrow, ws, accumulate=True, activation="clamped_swish",
+                                           limit=7.0, identity_w=idw), flush)
+        record(f"experts_clamped_{tag}", t, bytes_=distinct * 3 * W * eff * 2 + T * W * (2 + 8),
+               tensor_flops=2.0 * pairs * 3 * W * eff)
+        out[f"experts_clamped_{tag}"]["distinct_experts"] = distinct
+        out[f"experts_clamped_{tag}"]["pairs_with_weights"] = pairs
+    return out
+
+
 def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, sizes=("small", "1B-like"), context=2048,
         prompt=2048, batches=(8, 64), kernels_at="1B-like", design="kugilix") -> dict:
     """``build_engine(cfg, batch, context, extra_tokens)``, ``time_decode`` and ``time_prefill`` are bench.py's.
-    ``design`` "kugilix": that design beside Qwen2; "nusudra" or "netinex": that design beside both."""
+    ``design`` "kugilix": that design beside Qwen2; "nusudra" or "netinex": that design beside both; "sumevik": that
+    design beside Netinex and Qwen2."""
     import torch
 
     result = {"context": context, "prompt_tokens": prompt, "window": WINDOW, "sizes": {}}
@@ -492,6 +676,8 @@ def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, size
             designs = (("nusudra", nusudra_config(s)),) + designs
         if design == "netinex":
             designs = (("netinex", netinex_config(s)),) + designs
+        if design == "sumevik":
+            designs = (("sumevik", sumevik_config(s)), ("netinex", netinex_config(s)), ("qwen2", qwen2_config(s)))
         for design_name, cfg in designs:
             numbers = {}
             engine = build_engine(cfg, 1, context, extra_tokens=prompt)
@@ -511,7 +697,13 @@ def run(build_engine, time_decode, time_prefill, peaks, steps=32, warmup=4, size
                 torch.cuda.empty_cache()
             entry[design_name] = numbers
         result["sizes"][name] = entry
-    if kernels_at:
+    if kernels_at and design == "sumevik":
+        result["kernels_sumevik"] = {"at": kernels_at, "expert_ff": netinex_expert_ff(SIZES[kernels_at]), "experts": EXPERTS,
+                                     "identity": SUMEVIK_IDENTITY, "top": TOP,
+                                     **sumevik_kernel_numbers(SIZES[kernels_at], peaks)}
+        result["kernels_netinex"] = {"at": kernels_at, "expert_ff": netinex_expert_ff(SIZES[kernels_at]),
+                                     "experts": EXPERTS, "top": TOP, **netinex_kernel_numbers(SIZES[kernels_at], peaks)}
+    elif kernels_at:
         result["kernels"] = {"at": kernels_at, **kernel_numbers(SIZES[kernels_at], peaks)}
         if design == "nusudra":
             result["kernels_nusudra"] = {"at": kernels_at, **nusudra_kernel_numbers(SIZES[kernels_at], peaks)}

@@ -12,6 +12,12 @@
 // The plain form also takes a decay per ROW of the state (per key channel) that changes with every token, given as
 // fp32 numbers z per (token, head, row): the row's decay is sigmoid(z)^power = exp(-softplus(-z) * power), formed
 // in fp32 where the rows are staged; the decay per head is then left out (gated linear attention).
+// That form runs long portions of prompts as segments side by side, because the recurrence is linear in the state
+// (S_end = diag(product of the segment's decays) S_start + the segment's own sum): MODE 1 sums every segment but a
+// request's last from a zero state into scratch, with the products of its rows' decays; a combine kernel turns those
+// into the state at every segment's start; MODE 2 runs every segment from there and writes the outputs, a request's last
+// segment also its state.  A segment's place in scratch is (its first row / seg_len) + its request's index in the step,
+// which no two segments share.
 //
 // The columns of S do not depend on one another.  4, 8, 16 or 32 lanes (by the head's size) share a column, each
 // holding eight rows of it in registers (rows sub, sub + lanes, ...), and a block of 128 threads owns 32, 16, 8 or 4
@@ -78,12 +84,13 @@ __global__ void __launch_bounds__(128) recurrence_gates_kernel(const T* proj, in
 
 // LANES lanes share a column, GR_KPL rows each: dim <= GR_KPL * LANES.  AHEAD: the next tokens are requested into registers
 // while the present ones are worked on (portions of prompts); without it a stage goes straight to shared memory.
-template <typename T, int LANES, bool DELTA, bool AHEAD, bool ROWDECAY = false>
+template <typename T, int LANES, bool DELTA, bool AHEAD, bool ROWDECAY = false, int MODE = 0>
 __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     const T* q, int ldq, const T* k, int ldk, const T* v, int ldv, const float* decay, const float* beta,
     const float* qscale, const float* kscale, const float* __restrict__ skip, float* __restrict__ out, int ldo,
     float* state, const int* __restrict__ seq_q_start, const int* __restrict__ seq_state_slot, int heads, int qk_heads,
-    int dim, int vdim, int write_state, const float* row_z, int ldz, float row_power, float q_mul) {
+    int dim, int vdim, int write_state, const float* row_z, int ldz, float row_power, float q_mul, int seg_len = 0,
+    int segs_max = 1, float* scratch_s = nullptr, float* scratch_p = nullptr) {
     constexpr int COLS = GR_THREADS / LANES;  // columns of a block
     constexpr int STAGE = (ROWDECAY && LANES == 32) ? GR_STAGE / 2 : GR_STAGE;  // three staged vectors of 256 rows: fewer tokens
     constexpr int ROWS = GR_KPL * LANES;      // rows of the state that the lanes of a column hold
@@ -95,20 +102,34 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     __shared__ float as[ROWDECAY ? STAGE : 1][ROWDECAY ? ROWS : 1];  // the rows' decays of the staged tokens
     pdl_wait();
     pdl_launch_dependents();
-    const int seq = blockIdx.x, head = blockIdx.y;
+    const int seq = MODE ? blockIdx.x / segs_max : blockIdx.x, head = blockIdx.y;
     const int tid = threadIdx.x, sub = tid % LANES, cl = tid / LANES;
     const int col = blockIdx.z * COLS + cl;
     const bool active = col < vdim;
     const int qh = head / (heads / qk_heads);
-    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
     if (row1 <= row0) return;
     // the state lies transposed, [slot, head, vdim, dim]: the lanes of a column read consecutive floats
     float* S = state + (((size_t)seq_state_slot[seq] * heads + head) * vdim + (active ? col : 0)) * (size_t)dim;
+    float* S_from = S;
+    bool last_segment = true;
+    size_t place = 0;
+    if (MODE) {  // one segment of the request
+        const int first = row0 + (blockIdx.x % segs_max) * seg_len;
+        if (first >= row1) return;
+        last_segment = first + seg_len >= row1;
+        if (MODE == 1 && last_segment) return;  // nobody starts from the end of the last segment
+        place = (size_t)(first / seg_len + seq);
+        row0 = first, row1 = last_segment ? row1 : first + seg_len;
+        S_from = scratch_s + ((place * heads + head) * vdim + (active ? col : 0)) * (size_t)dim;
+    }
     float s[GR_KPL];
+    float pr[ROWDECAY && MODE == 1 ? GR_KPL : 1];  // MODE 1: the products of the rows' decays over the segment
 #pragma unroll
     for (int i = 0; i < GR_KPL; ++i) {
         const int kk = sub + LANES * i;
-        s[i] = (active && kk < dim) ? S[kk] : 0.0f;
+        s[i] = (MODE != 1 && active && kk < dim) ? S_from[kk] : 0.0f;
+        if (ROWDECAY && MODE == 1) pr[i] = 1.0f;
     }
     // rows of the staged vectors beyond the head's size stay zero
     for (int i = tid; i < STAGE * ROWS; i += GR_THREADS) {
@@ -227,6 +248,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 for (int i = 0; i < GR_KPL; i += 2) {
                     const float g0 = ROWDECAY ? as[r][sub + LANES * i] : g;
                     const float g1 = ROWDECAY ? as[r][sub + LANES * (i + 1)] : g;
+                    if (ROWDECAY && MODE == 1) pr[i] *= g0, pr[i + 1] *= g1;
                     s[i] = fmaf(g0, s[i], kr[i] * uk), s[i + 1] = fmaf(g1, s[i + 1], kr[i + 1] * uk);
                     od0 = fmaf(s[i], qr[i], od0), od1 = fmaf(s[i + 1], qr[i + 1], od1);
                 }
@@ -234,15 +256,52 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
             float od = od0 + od1;
 #pragma unroll
             for (int o = 1; o < LANES; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
-            if (sub == 0 && active) out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, (fq * q_mul) * od);
+            if (MODE != 1 && sub == 0 && active)
+                out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, (fq * q_mul) * od);
         }
     }
-    if (write_state && active) {
+    if (MODE == 1) {  // the segment's own sum, and (once per head) the products of its decays
+#pragma unroll
+        for (int i = 0; i < GR_KPL; ++i) {
+            const int kk = sub + LANES * i;
+            if (active && kk < dim) S_from[kk] = s[i];
+            if (ROWDECAY && blockIdx.z == 0 && cl == 0 && kk < dim) scratch_p[(place * heads + head) * (size_t)dim + kk] = pr[i];
+        }
+        return;
+    }
+    if (write_state && active && last_segment) {
 #pragma unroll
         for (int i = 0; i < GR_KPL; ++i) {
             const int kk = sub + LANES * i;
             if (kk < dim) S[kk] = s[i];
         }
+    }
+}
+
+// Between the two passes over segments: scratch_s holds every segment's own sum (but the last one's of a request);
+// afterwards it holds the state at every segment's start: S_start(0) = the request's state, S_start(n + 1) =
+// diag(products of segment n's decays) S_start(n) + sum(n).  A thread per element of a (request, head)'s state.
+__global__ void __launch_bounds__(256) row_decay_combine_kernel(float* scratch_s, const float* scratch_p, const float* state,
+                                                                const int* __restrict__ seq_q_start,
+                                                                const int* __restrict__ seq_state_slot, int heads, int dim,
+                                                                int vdim, int seg_len) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;  // column * dim + row
+    if (e >= vdim * dim) return;
+    const int row = e % dim;
+    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    if (row1 <= row0) return;
+    float s = state[((size_t)seq_state_slot[seq] * heads + head) * (size_t)vdim * dim + e];
+    for (int first = row0; first < row1; first += seg_len) {
+        const size_t place = (size_t)(first / seg_len + seq);
+        float* at = scratch_s + (place * heads + head) * (size_t)vdim * dim + e;
+        const bool last = first + seg_len >= row1;
+        const float own = last ? 0.0f : *at;
+        *at = s;
+        if (last) break;
+        s = fmaf(scratch_p[(place * heads + head) * (size_t)dim + row], s, own);
     }
 }
 
@@ -323,18 +382,20 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* o, i
     }
 }
 
-template <typename T, bool DELTA, bool AHEAD, bool ROWDECAY = false>
+template <typename T, bool DELTA, bool AHEAD, bool ROWDECAY = false, int MODE = 0>
 int launch_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const float* decay,
                       const float* beta, const float* qscale, const float* kscale, const float* skip, float* out, int ldo,
                       float* state, const int* seq_q_start, const int* seq_state_slot, int seqs, int heads, int qk_heads,
                       int dim, int vdim, int write_state, cudaStream_t s, const float* row_z = nullptr, int ldz = 0,
-                      float row_power = 1.0f, float q_mul = 1.0f) {
+                      float row_power = 1.0f, float q_mul = 1.0f, int seg_len = 0, int segs_max = 1,
+                      float* scratch_s = nullptr, float* scratch_p = nullptr) {
     const dim3 block(GR_THREADS);
 #define FERRIS_GR_LAUNCH(LANES)                                                                                         \
-    ferris_launch(gated_recurrence_kernel<T, LANES, DELTA, AHEAD, ROWDECAY>,                                          \
-                  dim3(seqs, heads, (vdim + GR_THREADS / LANES - 1) / (GR_THREADS / LANES)), block, 0, s, (const T*)q, \
-                  ldq, (const T*)k, ldk, (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo, state,          \
-                  seq_q_start, seq_state_slot, heads, qk_heads, dim, vdim, write_state, row_z, ldz, row_power, q_mul)
+    ferris_launch(gated_recurrence_kernel<T, LANES, DELTA, AHEAD, ROWDECAY, MODE>,                                    \
+                  dim3(seqs * segs_max, heads, (vdim + GR_THREADS / LANES - 1) / (GR_THREADS / LANES)), block, 0, s,   \
+                  (const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, decay, beta, qscale, kscale, skip, out, ldo,    \
+                  state, seq_q_start, seq_state_slot, heads, qk_heads, dim, vdim, write_state, row_z, ldz, row_power,   \
+                  q_mul, seg_len, segs_max, scratch_s, scratch_p)
     if (dim <= 32)
         FERRIS_GR_LAUNCH(4);
     else if (dim <= 64)
@@ -403,23 +464,35 @@ FERRIS_API int ferris_gated_recurrence(const void* q, int ldq, const void* k, in
 
 // The plain form with a decay per row of the state: row_z fp32 [tokens, heads x dim], rows ldz apart; the decay of
 // row r of head h at token t is sigmoid(row_z[t, h, r])^row_power.  q and k come in `heads` heads; out = q_mul S^T q.
+// segs_max > 1: no request brings more than segs_max * seg_len tokens, and they run as segments of seg_len side by side;
+// scratch_s: fp32 [(tokens / seg_len + seqs + 1), heads, vdim, dim], scratch_p: fp32 [the same places, heads, dim].
 FERRIS_API int ferris_row_decay_recurrence(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int dtype,
                                            const float* row_z, int ldz, float row_power, float q_mul, float* out, int ldo,
                                            float* state, const int* seq_q_start, const int* seq_state_slot, int seqs,
-                                           int heads, int dim, int vdim, int write_state, int longest, void* stream) {
+                                           int heads, int dim, int vdim, int write_state, int longest, int seg_len,
+                                           int segs_max, float* scratch_s, float* scratch_p, void* stream) {
     if (seqs <= 0) return FERRIS_OK;
     if (heads <= 0 || !row_z) FERRIS_REFUSE("row-decay recurrence: %d heads, or no decays", heads);
     if (dim <= 0 || dim > GR_MAX_DIM || vdim <= 0) FERRIS_REFUSE("row-decay recurrence: heads of %d x %d (at most %d rows)", dim, vdim, GR_MAX_DIM);
     if (heads > 65535 || (vdim + 3) / 4 > 65535) FERRIS_REFUSE("row-decay recurrence: too many heads or columns for one launch");
     if (dtype != FERRIS_F32 && dtype != FERRIS_BF16) FERRIS_REFUSE("row-decay recurrence: unknown dtype %d", dtype);
+    if (segs_max > 1 && (!scratch_s || !scratch_p || seg_len <= 0)) FERRIS_REFUSE("row-decay recurrence: segments need scratch and a length");
     cudaStream_t s = (cudaStream_t)stream;
     const bool ahead = longest > GR_STAGE;
-#define FERRIS_RD_GO(T, A)                                                                                                   \
-    return launch_recurrence<T, false, A, true>(q, ldq, k, ldk, v, ldv, nullptr, nullptr, nullptr, nullptr, nullptr, out, ldo, \
-                                                state, seq_q_start, seq_state_slot, seqs, heads, heads, dim, vdim, write_state, \
-                                                s, row_z, ldz, row_power, q_mul)
-    if (dtype == FERRIS_F32) { if (ahead) FERRIS_RD_GO(float, true); else FERRIS_RD_GO(float, false); }
-    if (ahead) FERRIS_RD_GO(bf16, true); else FERRIS_RD_GO(bf16, false);
+#define FERRIS_RD_GO(T, A, M)                                                                                                \
+    launch_recurrence<T, false, A, true, M>(q, ldq, k, ldk, v, ldv, nullptr, nullptr, nullptr, nullptr, nullptr, out, ldo,    \
+                                            state, seq_q_start, seq_state_slot, seqs, heads, heads, dim, vdim, write_state,  \
+                                            s, row_z, ldz, row_power, q_mul, seg_len, M ? segs_max : 1, scratch_s, scratch_p)
+    if (segs_max > 1) {  // segments side by side: sums, carry, outputs
+        int rc = dtype == FERRIS_F32 ? FERRIS_RD_GO(float, true, 1) : FERRIS_RD_GO(bf16, true, 1);
+        if (rc != FERRIS_OK) return rc;
+        const int elems = vdim * dim;
+        ferris_launch(row_decay_combine_kernel, dim3(seqs, heads, (elems + 255) / 256), dim3(256), 0, s, scratch_s,
+                      (const float*)scratch_p, (const float*)state, seq_q_start, seq_state_slot, heads, dim, vdim, seg_len);
+        return dtype == FERRIS_F32 ? FERRIS_RD_GO(float, true, 2) : FERRIS_RD_GO(bf16, true, 2);
+    }
+    if (dtype == FERRIS_F32) return ahead ? FERRIS_RD_GO(float, true, 0) : FERRIS_RD_GO(float, false, 0);
+    return ahead ? FERRIS_RD_GO(bf16, true, 0) : FERRIS_RD_GO(bf16, false, 0);
 #undef FERRIS_RD_GO
 }
 

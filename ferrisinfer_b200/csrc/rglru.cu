@@ -13,12 +13,14 @@
 // four quarters of the block take (their sums added in the runs' order).
 //
 // `rglru_scan`: s_t = a_t s_(t-1) + b_t is linear in s, so a run of tokens is summed up by (product of its a, its end
-// value from zero) and runs combine.  A block owns 32 channels of one request and walks its tokens in tiles of
+// value from zero) and runs combine.  A block owns SCAN_CH channels of one request and walks its tokens in tiles of
 // SEGS x SEG_TOKENS: a thread holds one run of SEG_TOKENS tokens of one channel in registers (all loads of a tile are
 // in flight together), forms the run's summary, the summaries meet in shared memory, every thread folds the runs
 // before its own onto the tile's incoming value, and then writes its tokens' outputs.  The chain of a tile is
 // SEG_TOKENS + SEGS + SEG_TOKENS steps instead of SEGS x SEG_TOKENS.  A step of single tokens is one thread per
-// (request, channel).
+// (request, channel); the gates kernel then takes that step itself (STEP): the thread that has formed a token's a and b
+// for a channel reads the channel's state, moves it on and writes the gated output, so a and b never reach memory and
+// the scan is no launch of its own.
 #include <math.h>
 
 #include "common.cuh"
@@ -26,7 +28,9 @@
 namespace {
 
 constexpr int RG_TOKENS = 8, RG_COLS = 64, RG_PARTS = 4, RG_THREADS = RG_COLS * RG_PARTS;
-constexpr int SCAN_CH = 32, SCAN_SEGS = 8, SCAN_SEG_TOKENS = 8, SCAN_THREADS = SCAN_CH * SCAN_SEGS;
+// eight channels a block (a 32-byte sector of the fp32 rows), 32 runs of eight tokens: a long prompt of a few thousand
+// channels fills the SMs, and a tile of 256 tokens costs a chain of 8 + 32 + 8 steps
+constexpr int SCAN_CH = 8, SCAN_SEGS = 32, SCAN_SEG_TOKENS = 8, SCAN_THREADS = SCAN_CH * SCAN_SEGS;
 
 __device__ __forceinline__ float softplus_r(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
 __device__ __forceinline__ float sigmoid_r(float v) { return 1.0f / (1.0f + expf(-v)); }
@@ -35,12 +39,16 @@ __device__ __forceinline__ float gelu_tanh_r(float z) {
 }
 
 // u: [tokens, C] rows ldu apart; wa, wi: [blocks, bs, bs] as [block][input][output]; ba, bi, sp (softplus(lam)): fp32 [C].
-template <typename T>
+// STEP (every request brings one token, row t is request t's): state, slots, the other branch y and the output rows
+// are given, a_out and b_out are not.
+template <typename T, bool STEP>
 __global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int ldu, const T* __restrict__ wa,
                                                                  const T* __restrict__ wi, const float* __restrict__ ba,
                                                                  const float* __restrict__ bi, const float* __restrict__ sp,
                                                                  float* __restrict__ a_out, float* __restrict__ b_out,
-                                                                 int tokens, int C, int bs, float decay_factor) {
+                                                                 int tokens, int C, int bs, float decay_factor, float* state,
+                                                                 const int* __restrict__ seq_state_slot, const T* y, int ldy,
+                                                                 T* __restrict__ out, int ldo, int act, int write_state) {
     extern __shared__ float us[];  // [RG_TOKENS][bs], then the parts' sums [RG_PARTS - 1][2][RG_TOKENS][RG_COLS]
     pdl_wait();
     pdl_launch_dependents();
@@ -94,9 +102,21 @@ __global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int
         }
         const float log_a = -rate * sigmoid_r(za + bias_a);
         const float gate = sigmoid_r(zi + bias_i);
-        const size_t at = (size_t)(t0 + r) * C + c;
-        a_out[at] = expf(log_a);
-        b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gate * us[r * bs + n];
+        const float a = expf(log_a), b = sqrtf(-expm1f(2.0f * log_a)) * gate * us[r * bs + n];
+        if (STEP) {
+            float* S = state + (size_t)seq_state_slot[t0 + r] * C + c;
+            const float s_new = fmaf(a, *S, b);
+            if (write_state) *S = s_new;
+            float v = s_new;
+            if (y) {
+                const float z = to_float(y[(size_t)(t0 + r) * ldy + c]);
+                v *= act ? gelu_tanh_r(z) : z;
+            }
+            out[(size_t)(t0 + r) * ldo + c] = from_float<T>(v);
+        } else {
+            const size_t at = (size_t)(t0 + r) * C + c;
+            a_out[at] = a, b_out[at] = b;
+        }
     }
 }
 
@@ -181,29 +201,37 @@ __global__ void __launch_bounds__(256) rglru_scan_single_kernel(const float* a, 
 
 // u: [tokens, C] in the activations' type, rows ldu apart; wa, wi: [blocks, C / blocks, C / blocks] in the same type,
 // TRANSPOSED ([block][input][output]); ba, bi, sp: fp32 [C] (sp = softplus of the decay's parameter); a_out, b_out: fp32
-// [tokens, C]; decay_factor: the constant c of log a = -c r softplus(lam).
+// [tokens, C]; decay_factor: the constant c of log a = -c r softplus(lam).  With `state` (fp32 [slots, C]; a step in
+// which request t brings row t alone): a_out and b_out are not written; the state of slot seq_state_slot[t] moves on
+// (if write_state) and out[t] = s * act(y[t]) as in ferris_rglru_scan.
 FERRIS_API int ferris_rglru_gates(const void* u, int ldu, int dtype, const void* wa, const void* wi, const float* ba,
                                   const float* bi, const float* sp, float* a_out, float* b_out, int tokens, int C,
-                                  int blocks, float decay_factor, void* stream) {
+                                  int blocks, float decay_factor, float* state, const int* seq_state_slot, const void* y,
+                                  int ldy, void* out, int ldo, int act, int write_state, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (C <= 0 || blocks <= 0 || C % blocks || blocks > 65535) FERRIS_REFUSE("recurrent unit gates: %d channels in %d blocks", C, blocks);
+    const bool step = state != nullptr;  // a step of single tokens: the state moves on here
+    if (step ? (!seq_state_slot || !out) : (!a_out || !b_out)) FERRIS_REFUSE("recurrent unit gates: an output is missing");
     const int bs = C / blocks;
     const size_t smem = ((size_t)RG_TOKENS * bs + (size_t)(RG_PARTS - 1) * 2 * RG_TOKENS * RG_COLS) * sizeof(float);
     if (smem > 200 * 1024) FERRIS_REFUSE("recurrent unit gates: blocks of %d channels are more than shared memory holds", bs);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((tokens + RG_TOKENS - 1) / RG_TOKENS, blocks, (bs + RG_COLS - 1) / RG_COLS), block(RG_THREADS);
+    int e_;
+#define FERRIS_RG_RUN(T, STEP)                                                                                             \
+    do {                                                                                                                   \
+        if ((e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_kernel<T, STEP>, smem)) != FERRIS_OK) return e_;      \
+        ferris_launch(rglru_gates_kernel<T, STEP>, grid, block, smem, s, (const T*)u, ldu, (const T*)wa, (const T*)wi, ba, \
+                      bi, sp, a_out, b_out, tokens, C, bs, decay_factor, state, seq_state_slot, (const T*)y, ldy, (T*)out,  \
+                      ldo, act, write_state);                                                                              \
+    } while (0)
     if (dtype == FERRIS_F32) {
-        int e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_kernel<float>, smem);
-        if (e_ != FERRIS_OK) return e_;
-        ferris_launch(rglru_gates_kernel<float>, grid, block, smem, s, (const float*)u, ldu, (const float*)wa, (const float*)wi,
-                      ba, bi, sp, a_out, b_out, tokens, C, bs, decay_factor);
+        if (step) FERRIS_RG_RUN(float, true); else FERRIS_RG_RUN(float, false);
     } else if (dtype == FERRIS_BF16) {
-        int e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_kernel<bf16>, smem);
-        if (e_ != FERRIS_OK) return e_;
-        ferris_launch(rglru_gates_kernel<bf16>, grid, block, smem, s, (const bf16*)u, ldu, (const bf16*)wa, (const bf16*)wi, ba,
-                      bi, sp, a_out, b_out, tokens, C, bs, decay_factor);
+        if (step) FERRIS_RG_RUN(bf16, true); else FERRIS_RG_RUN(bf16, false);
     } else
         FERRIS_REFUSE("recurrent unit gates: unknown dtype %d", dtype);
+#undef FERRIS_RG_RUN
     FERRIS_LAUNCH_CHECK();
 }
 

@@ -1184,13 +1184,20 @@ def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torc
     )
 
 
+ROW_DECAY_SEGMENT = 128  # tokens of a segment where a long portion runs as segments side by side
+ROW_DECAY_SEGMENTS_FROM = 384  # the longest request of a step from which on that pays
+
+
 def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_z: torch.Tensor, power: float,
                          out: torch.Tensor, state: torch.Tensor, ctx, num_heads: int, head_dim: int, v_head_dim: int,
-                         q_scale: float = 1.0, write_state: bool = True):
+                         q_scale: float = 1.0, write_state: bool = True, segment: Optional[int] = None):
     """Linear attention with a decay per key channel that changes with every token: per head
     S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = q_scale S_t^T q_t, alpha_t = sigmoid(row_z[t])^power (fp32, formed in
     the kernel).  q, k: [T, heads x dim], v: [T, heads x vdim] (views with contiguous rows); row_z fp32 [T, heads x dim];
-    out fp32 [T, heads x vdim]; state fp32 [slots, heads, vdim, dim] (transposed), carried in the requests' slots."""
+    out fp32 [T, heads x vdim]; state fp32 [slots, heads, vdim, dim] (transposed), carried in the requests' slots.
+    A step whose longest request brings ROW_DECAY_SEGMENTS_FROM tokens or more (or any step, with ``segment`` given)
+    runs as segments of ``segment`` tokens side by side: a pass that sums each segment alone and multiplies up its
+    decays, one that carries the state from segment to segment, one that forms the outputs."""
     T, wq, ldq = _rows(q, "recurrence q")
     _, wk, ldk = _rows(k, "recurrence k")
     _, wv, ldv = _rows(v, "recurrence v")
@@ -1202,22 +1209,37 @@ def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_
             or state.shape[1:] != (num_heads, v_head_dim, head_dim)):
         raise KernelError(f"row-decay recurrence: q {tuple(q.shape)}, v {tuple(v.shape)}, decays {tuple(row_z.shape)}, "
                           f"state {tuple(state.shape)}")
+    longest = int(getattr(ctx, "max_q_len", 0) or T)
+    seg = int(segment or ROW_DECAY_SEGMENT)
+    segs_max = max(1, -(-longest // seg)) if (segment is not None or longest >= ROW_DECAY_SEGMENTS_FROM) else 1
+    scratch_s = scratch_p = None
+    if segs_max > 1:
+        places = T // seg + ctx.num_seqs + 1
+        ws = getattr(ctx, "workspace", None)
+        get = ws.get if ws is not None else (lambda name, shape, dtype: torch.empty(shape, dtype=dtype, device=q.device))
+        scratch_s = get("row_decay_segments", (places * num_heads * v_head_dim * head_dim,), torch.float32)
+        scratch_p = get("row_decay_products", (places * num_heads * head_dim,), torch.float32)
     _check(
         _lib().ferris_row_decay_recurrence(_ptr(q), _c_int(ldq), _ptr(k), _c_int(ldk), _ptr(v), _c_int(ldv),
                                            _c_int(_dt(q, "recurrence")), _ptr(row_z), _c_int(ldz), _c_float(power),
                                            _c_float(q_scale), _ptr(out), _c_int(ldo), _ptr(state), _ptr(ctx.seq_q_start),
                                            _ptr(ctx.seq_state_slot), _c_int(ctx.num_seqs), _c_int(num_heads),
                                            _c_int(head_dim), _c_int(v_head_dim), _c_int(1 if write_state else 0),
-                                           _c_int(int(getattr(ctx, "max_q_len", 0))), _stream()),
-        "row-decay recurrence",
+                                           _c_int(longest), _c_int(seg), _c_int(segs_max), _ptr(scratch_s), _ptr(scratch_p),
+                                           _stream()),
+        "row-decay recurrence", 1 if segs_max == 1 else 3,
     )
 
 
 def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
-                softplus_lam: torch.Tensor, a_out: torch.Tensor, b_out: torch.Tensor, decay_factor: float):
+                softplus_lam: torch.Tensor, a_out: Optional[torch.Tensor], b_out: Optional[torch.Tensor], decay_factor: float,
+                step: Optional[tuple] = None):
     """The gates of a gated linear recurrent unit: per block n of the channels r = sigmoid(Ra[n] u_n + ba),
     i = sigmoid(Ri[n] u_n + bi); a = exp(-decay_factor r softplus_lam); b = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t``:
-    [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out, b_out fp32 [T, C]."""
+    [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out, b_out fp32 [T, C].
+    ``step`` = (state fp32 [slots, C], ctx, y or None, out, gelu, write_state) for a step in which every request brings
+    one token: the kernel moves the state on itself and writes out = s * act(y) (see ``rglru_scan``); a_out and b_out
+    are then not needed."""
     T, C, ldu = _rows(u, "recurrent unit input")
     _need(wa_t, "recurrence gate matrices", u.dtype)
     _need(wi_t, "input gate matrices", u.dtype)
@@ -1225,14 +1247,32 @@ def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: tor
     bs = C // max(blocks, 1)
     for t_, name in ((ba, "recurrence gate bias"), (bi, "input gate bias"), (softplus_lam, "decay rates")):
         _need(t_, name, torch.float32)
-    _need(a_out, "decays", torch.float32)
-    _need(b_out, "gated inputs", torch.float32)
+    state = slots = y = out = None
+    ldy = ldo = 0
+    gelu = write_state = False
+    if step is not None:
+        state, ctx, y, out, gelu, write_state = step
+        _need(state, "recurrent state", torch.float32)
+        _, Co, ldo = _rows(out, "recurrent unit output")
+        if y is not None:
+            _, Cy, ldy = _rows(y, "recurrent unit branch")
+        if (T != ctx.num_seqs or state.dim() != 2 or state.shape[1] != C or out.shape != (T, C) or out.dtype != u.dtype
+                or (y is not None and (y.shape != (T, C) or y.dtype != u.dtype))):
+            raise KernelError(f"recurrent unit step: {T} rows of {ctx.num_seqs} requests, state {tuple(state.shape)}")
+        slots = ctx.seq_state_slot
+    else:
+        _need(a_out, "decays", torch.float32)
+        _need(b_out, "gated inputs", torch.float32)
+        if a_out.shape != (T, C) or b_out.shape != (T, C):
+            raise KernelError(f"recurrent unit gates: outputs {tuple(a_out.shape)}, {tuple(b_out.shape)} for {T} x {C}")
     if (wa_t.shape != (blocks, bs, bs) or wi_t.shape != wa_t.shape or blocks * bs != C or ba.numel() != C or bi.numel() != C
-            or softplus_lam.numel() != C or a_out.shape != (T, C) or b_out.shape != (T, C)):
+            or softplus_lam.numel() != C):
         raise KernelError(f"recurrent unit gates: u {tuple(u.shape)}, matrices {tuple(wa_t.shape)}")
     _check(_lib().ferris_rglru_gates(_ptr(u), _c_int(ldu), _c_int(_dt(u, "recurrent unit")), _ptr(wa_t), _ptr(wi_t), _ptr(ba),
                                      _ptr(bi), _ptr(softplus_lam), _ptr(a_out), _ptr(b_out), _c_int(T), _c_int(C),
-                                     _c_int(blocks), _c_float(decay_factor), _stream()), "recurrent unit gates")
+                                     _c_int(blocks), _c_float(decay_factor), _ptr(state), _ptr(slots), _ptr(y), _c_int(ldy),
+                                     _ptr(out), _c_int(ldo), _c_int(1 if gelu else 0), _c_int(1 if write_state else 0),
+                                     _stream()), "recurrent unit gates")
 
 
 def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], out: torch.Tensor, state: torch.Tensor, ctx,

@@ -248,10 +248,15 @@ class GatedLinearUnit(Mixer):
         u = ws.get("recurrent_conv", (T, C), ctx.act_dtype)
         ops.short_conv(proj[:, C:2 * C], u, self.conv_weight, None if history is None else history.state, ctx,
                        advance=owns_cache, bias=self.conv_bias, residual=False, silu=False)
-        a, b = ws.get("recurrent_unit_a", (T, C), torch.float32), ws.get("recurrent_unit_b", (T, C), torch.float32)
-        ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, a, b, self.decay_factor)
         y = ws.get("recurrent_gated", (T, C), ctx.act_dtype)
-        ops.rglru_scan(a, b, proj[:, :C], y, state.state, ctx, gelu=self.activation == "gelu_tanh", write_state=owns_cache)
+        gelu = self.activation == "gelu_tanh"
+        if ctx.max_q_len == 1 and T == ctx.num_seqs:  # single tokens: the gates kernel moves the state on itself
+            ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, None, None, self.decay_factor,
+                            step=(state.state, ctx, proj[:, :C], y, gelu, owns_cache))
+        else:
+            a, b = ws.get("recurrent_unit_a", (T, C), torch.float32), ws.get("recurrent_unit_b", (T, C), torch.float32)
+            ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, a, b, self.decay_factor)
+            ops.rglru_scan(a, b, proj[:, :C], y, state.state, ctx, gelu=gelu, write_state=owns_cache)
         ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
 
 

@@ -292,6 +292,36 @@ def test_gated_linear_attention_whole_in_portions_and_token_by_token(device, H, 
             assert torch.allclose(state[1].cpu().double().transpose(1, 2), last, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,d,dv,segment", [(2, 16, 32, 16), (1, 40, 8, 128), (3, 64, 24, 50), (1, 136, 16, 128)])
+def test_row_decay_recurrence_in_segments_side_by_side(device, H, d, dv, segment, dtype):
+    """Long portions as segments side by side (sums, carry, outputs) against the same requests token after token:
+    three requests of unequal length in one step, over slots out of order and from states that are not zero; one of
+    them shorter than a segment, one an exact multiple."""
+    ops = _ops()
+    torch.manual_seed(H * d + segment)
+    lengths, slots = [3 * segment, 5, 2 * segment + 7], [3, 0, 1]
+    T = sum(lengths)
+    q, k = (torch.randn(T, H * d) / math.sqrt(d)).to(dtype), (torch.randn(T, H * d) / math.sqrt(d)).to(dtype)
+    v = torch.randn(T, H * dv).to(dtype)
+    z = 2.0 + 2.0 * torch.randn(T, H * d)
+    start = torch.randn(5, H, dv, d)
+    rows = torch.cat([q, k, v], dim=1).to(device)
+    views = (rows[:, :H * d], rows[:, H * d:2 * H * d], rows[:, 2 * H * d:])
+    ctx = fake_ctx(device, lengths, [0, 0, 0], slots)
+    want, want_state = torch.empty(T, H * dv, device=device), start.clone().to(device)
+    ops.row_decay_recurrence(*views, z.to(device), 0.25, want, want_state, ctx, H, d, dv, q_scale=0.5)
+    got, got_state = torch.empty(T, H * dv, device=device), start.clone().to(device)
+    ops.row_decay_recurrence(*views, z.to(device), 0.25, got, got_state, ctx, H, d, dv, q_scale=0.5, segment=segment)
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= 2e-5 * scale
+    assert torch.allclose(got_state, want_state, atol=2e-5 * float(want_state.abs().max()))
+    kept = torch.empty(T, H * dv, device=device)  # without writing the state: the slots stay as they were
+    ops.row_decay_recurrence(*views, z.to(device), 0.25, kept, got_state, ctx, H, d, dv, q_scale=0.5, write_state=False,
+                             segment=segment)
+    assert torch.allclose(got_state, want_state, atol=2e-5 * float(want_state.abs().max()))
+
+
 def test_linear_attention_reads_a_write_from_hundreds_of_tokens_ago_along_a_channel_that_does_not_decay(device):
     """Key channel 0 keeps everything (its decay is sigmoid(40)^(1/tau) = 1), the other channels forget quickly: what
     token 3 wrote along channel 0 is read 600 tokens later by a query along channel 0, while every other token writes
