@@ -483,13 +483,14 @@ FERRIS_API int ferris_row_decay_recurrence(const void* q, int ldq, const void* k
     launch_recurrence<T, false, A, true, M>(q, ldq, k, ldk, v, ldv, nullptr, nullptr, nullptr, nullptr, nullptr, out, ldo,    \
                                             state, seq_q_start, seq_state_slot, seqs, heads, heads, dim, vdim, write_state,  \
                                             s, row_z, ldz, row_power, q_mul, seg_len, M ? segs_max : 1, scratch_s, scratch_p)
-    if (segs_max > 1) {  // segments side by side: sums, carry, outputs
-        int rc = dtype == FERRIS_F32 ? FERRIS_RD_GO(float, true, 1) : FERRIS_RD_GO(bf16, true, 1);
+    if (segs_max > 1) {  // segments side by side: sums, carry, outputs.  Many blocks hide one another's loads, so a stage
+        // goes straight to shared memory: the form that requests the next tokens into registers holds four blocks an SM
+        int rc = dtype == FERRIS_F32 ? FERRIS_RD_GO(float, false, 1) : FERRIS_RD_GO(bf16, false, 1);
         if (rc != FERRIS_OK) return rc;
         const int elems = vdim * dim;
         ferris_launch(row_decay_combine_kernel, dim3(seqs, heads, (elems + 255) / 256), dim3(256), 0, s, scratch_s,
                       (const float*)scratch_p, (const float*)state, seq_q_start, seq_state_slot, heads, dim, vdim, seg_len);
-        return dtype == FERRIS_F32 ? FERRIS_RD_GO(float, true, 2) : FERRIS_RD_GO(bf16, true, 2);
+        return dtype == FERRIS_F32 ? FERRIS_RD_GO(float, false, 2) : FERRIS_RD_GO(bf16, false, 2);
     }
     if (dtype == FERRIS_F32) return ahead ? FERRIS_RD_GO(float, true, 0) : FERRIS_RD_GO(float, false, 0);
     return ahead ? FERRIS_RD_GO(bf16, true, 0) : FERRIS_RD_GO(bf16, false, 0);

@@ -192,9 +192,11 @@ def random_ids(vocab: int, n: int, seed: int) -> list:
 CLOSE_CALL = 0.03  # of a router's scores, which add up to one (bfloat16 inputs move a score of 0.5 by some 0.02)
 
 
-def safe_sequence(cfg: dict, weights: dict, n: int, seed: int):
+def safe_sequence(cfg: dict, weights: dict, n: int, seed: int, close_call: float = None):
     """(ids, float64 logits [n, vocab]) of a random sequence in which no router's choice is a close call: token by
-    token, a token whose choice at some layer lies within ``CLOSE_CALL`` of turning is drawn again."""
+    token, a token whose choice at some layer lies within ``close_call`` (``CLOSE_CALL`` unless given: with many router
+    outputs the scores and their gaps are smaller, and so is what rounding moves them by) of turning is drawn again."""
+    close_call = CLOSE_CALL if close_call is None else close_call
     rng = random.Random(seed)
     w64 = {k: v.to(torch.float64) for k, v in weights.items()}
     plain_cfg = folder_config(cfg)
@@ -204,7 +206,7 @@ def safe_sequence(cfg: dict, weights: dict, n: int, seed: int):
             tok = rng.randrange(cfg["vocab"])
             margins = []
             logits, new_state = plain.forward(plain_cfg, w64, [tok], start=t, state=state, margins=margins)
-            if not margins or min(margins) >= CLOSE_CALL:
+            if not margins or min(margins) >= close_call:
                 break
         else:
             raise AssertionError(f"no token without a close call at position {t}")
