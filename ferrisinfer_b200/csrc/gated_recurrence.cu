@@ -11,10 +11,15 @@
 // the factor is 1 / |x|, formed in fp32 by the gates kernel, so that the vectors themselves are read once as stored).
 // The plain form also takes a decay per ROW of the state (per key channel) that changes with every token, given as
 // fp32 numbers z per (token, head, row): the row's decay is sigmoid(z)^power = exp(-softplus(-z) * power), formed
-// in fp32 where the rows are staged; the decay per head is then left out (gated linear attention).
+// in fp32 where the rows are staged; the decay per head is then left out (gated linear attention).  What is staged is
+// the decay MINUS ONE, expm1(-softplus(-z) power), and a row moves on as s + ((decay - 1) s + k u): a decay close to one
+// rounded to 24 bits is off by a fixed share of what it takes away, with the same sign at every step where the row's
+// decay hardly changes, which over a thousand tokens shows in 32-bit logits; this way only the sum rounds, at the state's
+// size, up as often as down.
 // That form runs long portions of prompts as segments side by side, because the recurrence is linear in the state
 // (S_end = diag(product of the segment's decays) S_start + the segment's own sum): MODE 1 sums every segment but a
-// request's last from a zero state into scratch, with the products of its rows' decays; a combine kernel turns those
+// request's last from a zero state into scratch; a kernel of its own multiplies up the rows' decays over each segment
+// (as expm1 of the sum of their logarithms); a combine kernel turns those
 // into the state at every segment's start; MODE 2 runs every segment from there and writes the outputs, a request's last
 // segment also its state.  A segment's place in scratch is (its first row / seg_len) + its request's index in the step,
 // which no two segments share.
@@ -99,7 +104,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     __shared__ float ks[STAGE][ROWS];
     __shared__ float vs[STAGE][COLS];
     __shared__ float gs[STAGE], bs[STAGE], fqs[STAGE], fks[STAGE];
-    __shared__ float as[ROWDECAY ? STAGE : 1][ROWDECAY ? ROWS : 1];  // the rows' decays of the staged tokens
+    __shared__ float as[ROWDECAY ? STAGE : 1][ROWDECAY ? ROWS : 1];  // the rows' decays minus one of the staged tokens
     pdl_wait();
     pdl_launch_dependents();
     const int seq = MODE ? blockIdx.x / segs_max : blockIdx.x, head = blockIdx.y;
@@ -124,12 +129,10 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
         S_from = scratch_s + ((place * heads + head) * vdim + (active ? col : 0)) * (size_t)dim;
     }
     float s[GR_KPL];
-    float pr[ROWDECAY && MODE == 1 ? GR_KPL : 1];  // MODE 1: the products of the rows' decays over the segment
 #pragma unroll
     for (int i = 0; i < GR_KPL; ++i) {
         const int kk = sub + LANES * i;
         s[i] = (MODE != 1 && active && kk < dim) ? S_from[kk] : 0.0f;
-        if (ROWDECAY && MODE == 1) pr[i] = 1.0f;
     }
     // rows of the staged vectors beyond the head's size stay zero
     for (int i = tid; i < STAGE * ROWS; i += GR_THREADS) {
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 const size_t row = (size_t)(t0 + r);
                 qs[r][c] = to_float(q[row * ldq + (size_t)qh * dim + c]);
                 ks[r][c] = to_float(k[row * ldk + (size_t)qh * dim + c]);
-                if (ROWDECAY) as[r][c] = expf(-softplus_g(-row_z[row * ldz + (size_t)head * dim + c]) * row_power);
+                if (ROWDECAY) as[r][c] = expm1f(-softplus_g(-row_z[row * ldz + (size_t)head * dim + c]) * row_power);
             }
             for (int i = tid; i < n * COLS; i += GR_THREADS) {
                 const int r = i / COLS, c = i - r * COLS;
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 const int c = tid + j * GR_THREADS;
                 if (c < dim) {
                     qs[r][c] = to_float(pq[r][j]), ks[r][c] = to_float(pk[r][j]);
-                    if (ROWDECAY) as[r][c] = expf(-softplus_g(-pz[r][j]) * row_power);
+                    if (ROWDECAY) as[r][c] = expm1f(-softplus_g(-pz[r][j]) * row_power);
                 }
             }
         }
@@ -246,10 +249,12 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 uk = (b * vv) * fk;
 #pragma unroll
                 for (int i = 0; i < GR_KPL; i += 2) {
-                    const float g0 = ROWDECAY ? as[r][sub + LANES * i] : g;
-                    const float g1 = ROWDECAY ? as[r][sub + LANES * (i + 1)] : g;
-                    if (ROWDECAY && MODE == 1) pr[i] *= g0, pr[i + 1] *= g1;
-                    s[i] = fmaf(g0, s[i], kr[i] * uk), s[i + 1] = fmaf(g1, s[i + 1], kr[i + 1] * uk);
+                    if (ROWDECAY) {  // s + ((decay - 1) s + k u)
+                        s[i] += fmaf(as[r][sub + LANES * i], s[i], kr[i] * uk);
+                        s[i + 1] += fmaf(as[r][sub + LANES * (i + 1)], s[i + 1], kr[i + 1] * uk);
+                    } else {
+                        s[i] = fmaf(g, s[i], kr[i] * uk), s[i + 1] = fmaf(g, s[i + 1], kr[i + 1] * uk);
+                    }
                     od0 = fmaf(s[i], qr[i], od0), od1 = fmaf(s[i + 1], qr[i + 1], od1);
                 }
             }
@@ -260,12 +265,11 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
                 out[(size_t)(t0 + r) * ldo + (size_t)head * vdim + col] = fmaf(d_skip, vv, (fq * q_mul) * od);
         }
     }
-    if (MODE == 1) {  // the segment's own sum, and (once per head) the products of its decays
+    if (MODE == 1) {  // the segment's own sum
 #pragma unroll
         for (int i = 0; i < GR_KPL; ++i) {
             const int kk = sub + LANES * i;
             if (active && kk < dim) S_from[kk] = s[i];
-            if (ROWDECAY && blockIdx.z == 0 && cl == 0 && kk < dim) scratch_p[(place * heads + head) * (size_t)dim + kk] = pr[i];
         }
         return;
     }
@@ -278,9 +282,30 @@ __global__ void __launch_bounds__(GR_THREADS) gated_recurrence_kernel(
     }
 }
 
+// The product of every row's decays over a segment, minus one: expm1 of the sum of the logarithms -softplus(-z) power.
+// A block per (request, segment) and head, a thread per row; the last segment of a request has no use for it.
+__global__ void __launch_bounds__(256) row_decay_products_kernel(const float* row_z, int ldz, float row_power,
+                                                                 float* __restrict__ scratch_p,
+                                                                 const int* __restrict__ seq_q_start, int heads, int dim,
+                                                                 int seg_len, int segs_max) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x / segs_max, head = blockIdx.y;
+    const int row0 = seq_q_start[seq], row1 = seq_q_start[seq + 1];
+    const int first = row0 + (blockIdx.x % segs_max) * seg_len;
+    if (first >= row1 || first + seg_len >= row1) return;
+    const size_t place = (size_t)(first / seg_len + seq);
+    for (int r = threadIdx.x; r < dim; r += blockDim.x) {
+        float sum = 0.0f;
+        for (int t = first; t < first + seg_len; ++t) sum -= softplus_g(-row_z[(size_t)t * ldz + (size_t)head * dim + r]) * row_power;
+        scratch_p[(place * heads + head) * (size_t)dim + r] = expm1f(sum);
+    }
+}
+
 // Between the two passes over segments: scratch_s holds every segment's own sum (but the last one's of a request);
 // afterwards it holds the state at every segment's start: S_start(0) = the request's state, S_start(n + 1) =
-// diag(products of segment n's decays) S_start(n) + sum(n).  A thread per element of a (request, head)'s state.
+// diag(products of segment n's decays) S_start(n) + sum(n), the products given minus one.  A thread per element of a
+// (request, head)'s state.
 __global__ void __launch_bounds__(256) row_decay_combine_kernel(float* scratch_s, const float* scratch_p, const float* state,
                                                                 const int* __restrict__ seq_q_start,
                                                                 const int* __restrict__ seq_state_slot, int heads, int dim,
@@ -301,7 +326,7 @@ __global__ void __launch_bounds__(256) row_decay_combine_kernel(float* scratch_s
         const float own = last ? 0.0f : *at;
         *at = s;
         if (last) break;
-        s = fmaf(scratch_p[(place * heads + head) * (size_t)dim + row], s, own);
+        s += fmaf(scratch_p[(place * heads + head) * (size_t)dim + row], s, own);
     }
 }
 
@@ -487,6 +512,8 @@ FERRIS_API int ferris_row_decay_recurrence(const void* q, int ldq, const void* k
         // goes straight to shared memory: the form that requests the next tokens into registers holds four blocks an SM
         int rc = dtype == FERRIS_F32 ? FERRIS_RD_GO(float, false, 1) : FERRIS_RD_GO(bf16, false, 1);
         if (rc != FERRIS_OK) return rc;
+        ferris_launch(row_decay_products_kernel, dim3(seqs * segs_max, heads), dim3(dim >= 128 ? 256 : 64), 0, s, row_z, ldz,
+                      row_power, scratch_p, seq_q_start, heads, dim, seg_len, segs_max);
         const int elems = vdim * dim;
         ferris_launch(row_decay_combine_kernel, dim3(seqs, heads, (elems + 255) / 256), dim3(256), 0, s, scratch_s,
                       (const float*)scratch_p, (const float*)state, seq_q_start, seq_state_slot, heads, dim, vdim, seg_len);

@@ -7,13 +7,17 @@
 // nothing), s: fp32 [slots, C], zero when a request is admitted.  Two kernels.
 //
 // `rglru_gates`: the two block-diagonal products with fp32 sums, the sigmoids, the decay and the input's factor, all
-// fp32: it leaves a and b = sqrt(1 - a^2) i u per (token, channel).  1 - a^2 is formed as -expm1(2 log a), so that a
-// decay close to one keeps its digits.  The matrices lie transposed ([blocks, in, out]) so that the threads of a
+// fp32: it leaves log a and b = sqrt(1 - a^2) i u per (token, channel).  1 - a^2 is formed as -expm1(2 log a), so that a
+// decay close to one keeps its digits.  For the same reason the state moves on as s + (expm1(log a) s + b) and never
+// through a itself: a decay of 0.9995 rounded to 24 bits is off by up to 3e-8, a ten-thousandth of what it takes away
+// from the state, and where a channel's decay hardly changes from token to token that error has the same sign at
+// every step: over a thousand tokens it shows in 32-bit logits.  expm1(log a) s has the relative error of one rounding,
+// and the sum rounds at the state's size, sometimes up and sometimes down.  The matrices lie transposed ([blocks, in, out]) so that the threads of a
 // block read consecutive weights; eight tokens share one pass over them, and the inputs are cut into four runs that
 // four quarters of the block take (their sums added in the runs' order).
 //
-// `rglru_scan`: s_t = a_t s_(t-1) + b_t is linear in s, so a run of tokens is summed up by (product of its a, its end
-// value from zero) and runs combine.  A block owns SCAN_CH channels of one request and walks its tokens in tiles of
+// `rglru_scan`: s_t = a_t s_(t-1) + b_t is linear in s, so a run of tokens is summed up by (product of its a, kept as
+// expm1 of the sum of its log a; its end value from zero) and runs combine.  A block owns SCAN_CH channels of one request and walks its tokens in tiles of
 // SEGS x SEG_TOKENS: a thread holds one run of SEG_TOKENS tokens of one channel in registers (all loads of a tile are
 // in flight together), forms the run's summary, the summaries meet in shared memory, every thread folds the runs
 // before its own onto the tile's incoming value, and then writes its tokens' outputs.  The chain of a tile is
@@ -102,10 +106,11 @@ __global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int
         }
         const float log_a = -rate * sigmoid_r(za + bias_a);
         const float gate = sigmoid_r(zi + bias_i);
-        const float a = expf(log_a), b = sqrtf(-expm1f(2.0f * log_a)) * gate * us[r * bs + n];
+        const float b = sqrtf(-expm1f(2.0f * log_a)) * gate * us[r * bs + n];
         if (STEP) {
             float* S = state + (size_t)seq_state_slot[t0 + r] * C + c;
-            const float s_new = fmaf(a, *S, b);
+            const float s_old = *S;
+            const float s_new = s_old + fmaf(expm1f(log_a), s_old, b);
             if (write_state) *S = s_new;
             float v = s_new;
             if (y) {
@@ -115,12 +120,13 @@ __global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int
             out[(size_t)(t0 + r) * ldo + c] = from_float<T>(v);
         } else {
             const size_t at = (size_t)(t0 + r) * C + c;
-            a_out[at] = a, b_out[at] = b;
+            a_out[at] = log_a, b_out[at] = b;
         }
     }
 }
 
-// a, b: fp32 [tokens, C]; y: [tokens, C] rows ldy apart (null: the state itself is the output); out: rows ldo apart.
+// a: fp32 [tokens, C], the LOGARITHMS of the decays; b: fp32 [tokens, C]; y: [tokens, C] rows ldy apart (null: the state
+// itself is the output); out: rows ldo apart.
 template <typename T>
 __global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(const float* a, const float* b, const T* y, int ldy,
                                                                   T* __restrict__ out, int ldo, float* state,
@@ -145,20 +151,24 @@ __global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(const float* a
 #pragma unroll
         for (int j = 0; j < SCAN_SEG_TOKENS; ++j) {
             const bool in = live && first + j < row1;
-            av[j] = in ? a[(size_t)(first + j) * C + c] : 1.0f;
+            av[j] = in ? a[(size_t)(first + j) * C + c] : 0.0f;
             bv[j] = in ? b[(size_t)(first + j) * C + c] : 0.0f;
         }
-        float p = 1.0f, s = 0.0f;  // the run from zero: its product of decays and its end value
+        float log_p = 0.0f, s = 0.0f;  // the run from zero: the logarithm of its product of decays, and its end value
 #pragma unroll
-        for (int j = 0; j < SCAN_SEG_TOKENS; ++j) p *= av[j], s = fmaf(av[j], s, bv[j]);
-        prod[seg][lane] = p, last[seg][lane] = s;
+        for (int j = 0; j < SCAN_SEG_TOKENS; ++j) {
+            log_p += av[j];
+            av[j] = expm1f(av[j]);  // from here on: the decay minus one
+            s += fmaf(av[j], s, bv[j]);
+        }
+        prod[seg][lane] = expm1f(log_p), last[seg][lane] = s;
         __syncthreads();  // also: the carry of the tile before (or the state) is written
         float in_value = carry[lane];
-        for (int g = 0; g < seg; ++g) in_value = fmaf(prod[g][lane], in_value, last[g][lane]);
+        for (int g = 0; g < seg; ++g) in_value += fmaf(prod[g][lane], in_value, last[g][lane]);
         s = in_value;
 #pragma unroll
         for (int j = 0; j < SCAN_SEG_TOKENS; ++j) {
-            s = fmaf(av[j], s, bv[j]);
+            s += fmaf(av[j], s, bv[j]);
             if (live && first + j < row1) {
                 float v = s;
                 if (y) {
@@ -169,7 +179,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) rglru_scan_kernel(const float* a
             }
         }
         __syncthreads();  // everyone has read the carry and the summaries
-        if (seg == SCAN_SEGS - 1) carry[lane] = s;  // rows beyond the step's end pass the value on (a = 1, b = 0)
+        if (seg == SCAN_SEGS - 1) carry[lane] = s;  // rows beyond the step's end pass the value on (log a = 0, b = 0)
     }
     __syncthreads();
     if (write_state && live && seg == 0) *S = carry[lane];
@@ -187,7 +197,8 @@ __global__ void __launch_bounds__(256) rglru_scan_single_kernel(const float* a, 
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     float* S = state + (size_t)seq_state_slot[t] * C + c;
-    const float s = fmaf(a[(size_t)t * C + c], *S, b[(size_t)t * C + c]);
+    const float s_old = *S;
+    const float s = s_old + fmaf(expm1f(a[(size_t)t * C + c]), s_old, b[(size_t)t * C + c]);
     if (write_state) *S = s;
     float v = s;
     if (y) {
@@ -200,7 +211,7 @@ __global__ void __launch_bounds__(256) rglru_scan_single_kernel(const float* a, 
 }  // namespace
 
 // u: [tokens, C] in the activations' type, rows ldu apart; wa, wi: [blocks, C / blocks, C / blocks] in the same type,
-// TRANSPOSED ([block][input][output]); ba, bi, sp: fp32 [C] (sp = softplus of the decay's parameter); a_out, b_out: fp32
+// TRANSPOSED ([block][input][output]); ba, bi, sp: fp32 [C] (sp = softplus of the decay's parameter); a_out (log a), b_out: fp32
 // [tokens, C]; decay_factor: the constant c of log a = -c r softplus(lam).  With `state` (fp32 [slots, C]; a step in
 // which request t brings row t alone): a_out and b_out are not written; the state of slot seq_state_slot[t] moves on
 // (if write_state) and out[t] = s * act(y[t]) as in ferris_rglru_scan.
@@ -235,7 +246,7 @@ FERRIS_API int ferris_rglru_gates(const void* u, int ldu, int dtype, const void*
     FERRIS_LAUNCH_CHECK();
 }
 
-// a, b: fp32 [tokens, C]; y (may be null), out: the activations' type, rows ldy / ldo apart; state: fp32 [slots, C];
+// a (the logarithms of the decays), b: fp32 [tokens, C]; y (may be null), out: the activations' type, rows ldy / ldo apart; state: fp32 [slots, C];
 // act: 1 = the tanh form of GELU on y, 0 = y as it is.  single_tokens: every request brings one row (row t of request t).
 FERRIS_API int ferris_rglru_scan(const float* a, const float* b, const void* y, int ldy, void* out, int ldo, int dtype,
                                  float* state, const int* seq_q_start, const int* seq_state_slot, int tokens, int seqs,

@@ -1196,8 +1196,8 @@ def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_
     the kernel).  q, k: [T, heads x dim], v: [T, heads x vdim] (views with contiguous rows); row_z fp32 [T, heads x dim];
     out fp32 [T, heads x vdim]; state fp32 [slots, heads, vdim, dim] (transposed), carried in the requests' slots.
     A step whose longest request brings ROW_DECAY_SEGMENTS_FROM tokens or more (or any step, with ``segment`` given)
-    runs as segments of ``segment`` tokens side by side: a pass that sums each segment alone and multiplies up its
-    decays, one that carries the state from segment to segment, one that forms the outputs."""
+    runs as segments of ``segment`` tokens side by side: a pass that sums each segment alone, one that multiplies up
+    its rows' decays, one that carries the state from segment to segment, one that forms the outputs."""
     T, wq, ldq = _rows(q, "recurrence q")
     _, wk, ldk = _rows(k, "recurrence k")
     _, wv, ldv = _rows(v, "recurrence v")
@@ -1227,7 +1227,7 @@ def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_
                                            _c_int(head_dim), _c_int(v_head_dim), _c_int(1 if write_state else 0),
                                            _c_int(longest), _c_int(seg), _c_int(segs_max), _ptr(scratch_s), _ptr(scratch_p),
                                            _stream()),
-        "row-decay recurrence", 1 if segs_max == 1 else 3,
+        "row-decay recurrence", 1 if segs_max == 1 else 4,
     )
 
 
@@ -1235,8 +1235,9 @@ def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: tor
                 softplus_lam: torch.Tensor, a_out: Optional[torch.Tensor], b_out: Optional[torch.Tensor], decay_factor: float,
                 step: Optional[tuple] = None):
     """The gates of a gated linear recurrent unit: per block n of the channels r = sigmoid(Ra[n] u_n + ba),
-    i = sigmoid(Ri[n] u_n + bi); a = exp(-decay_factor r softplus_lam); b = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t``:
-    [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out, b_out fp32 [T, C].
+    i = sigmoid(Ri[n] u_n + bi); log a = -decay_factor r softplus_lam; b = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t``:
+    [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out (which receives log a,
+    not a: the scan never rounds a decay close to one to 24 bits) and b_out fp32 [T, C].
     ``step`` = (state fp32 [slots, C], ctx, y or None, out, gelu, write_state) for a step in which every request brings
     one token: the kernel moves the state on itself and writes out = s * act(y) (see ``rglru_scan``); a_out and b_out
     are then not needed."""
@@ -1277,9 +1278,10 @@ def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: tor
 
 def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: Optional[torch.Tensor], out: torch.Tensor, state: torch.Tensor, ctx,
                gelu: bool = True, write_state: bool = True):
-    """s_t = a_t s_(t-1) + b_t per (request, channel) from the request's slot of ``state`` (fp32 [slots, C]);
-    out_t = s_t * act(y_t), act the tanh form of GELU (``gelu``) or nothing; without ``y`` the state itself.  a, b fp32
-    [T, C]; y, out in the activations' type (views with contiguous rows)."""
+    """s_t = exp(a_t) s_(t-1) + b_t per (request, channel) from the request's slot of ``state`` (fp32 [slots, C]), formed as
+    s + (expm1(a_t) s + b_t); out_t = s_t * act(y_t), act the tanh form of GELU (``gelu``) or nothing; without ``y`` the
+    state itself.  a (the LOGARITHMS of the decays) and b fp32 [T, C]; y, out in the activations' type (views with
+    contiguous rows)."""
     _need(a, "decays", torch.float32)
     _need(b, "gated inputs", torch.float32)
     _need(state, "recurrent state", torch.float32)

@@ -213,19 +213,19 @@ def test_recurrent_unit_whole_in_portions_and_token_by_token(device, C, blocks, 
 
 
 def test_scan_carries_a_write_over_hundreds_of_tokens_and_several_requests(device):
-    """A decay of one everywhere but where a token writes: what token 3 wrote is read 700 tokens later, through tiles of
+    """A decay of one (a logarithm of zero) everywhere but where a token writes: what token 3 wrote is read 700 tokens later, through tiles of
     the scan, portions that end in the middle of a tile and single tokens; three requests of unequal length in one
     step, over slots out of order, each with its own write."""
     ops = _ops()
     C = 70
     lengths, slots = [704, 130, 1], [2, 0, 3]
     T = sum(lengths)
-    a = torch.ones(T, C)
+    a = torch.zeros(T, C)  # logarithms of the decays
     b = torch.zeros(T, C)
     starts = [0, 704, 834]
     marks = {0: 3, 1: 129, 2: 0}  # the token of each request that writes
     for s, t in marks.items():
-        a[starts[s] + t] = 0.25
+        a[starts[s] + t] = math.log(0.25)
         b[starts[s] + t] = torch.arange(C) + 10.0 * s + 1.0
     state = torch.full((5, C), 8.0, device=device)
     out = torch.empty(T, C, device=device)
@@ -234,8 +234,9 @@ def test_scan_carries_a_write_over_hundreds_of_tokens_and_several_requests(devic
     for s, t in marks.items():
         wrote = 0.25 * 8.0 + torch.arange(C) + 10.0 * s + 1.0
         rows = out[starts[s]:starts[s] + lengths[s]].cpu()
-        assert torch.equal(rows[:t], torch.full((t, C), 8.0)) and torch.equal(rows[t:], wrote.expand(lengths[s] - t, C))
-        assert torch.equal(state[slots[s]].cpu(), wrote)
+        assert torch.equal(rows[:t], torch.full((t, C), 8.0))
+        assert torch.allclose(rows[t:], wrote.expand(lengths[s] - t, C), rtol=1e-6, atol=0) and torch.equal(rows[t:], rows[t:t + 1].expand(lengths[s] - t, C))
+        assert torch.equal(state[slots[s]].cpu(), rows[-1])
     assert torch.equal(state[1].cpu(), torch.full((C,), 8.0)) and torch.equal(state[4].cpu(), torch.full((C,), 8.0))
     # the same in portions that end inside a tile, then single tokens
     state2 = torch.full((5, C), 8.0, device=device)
