@@ -105,6 +105,8 @@ class GroupedQueryAttention(Mixer):
             if self.output_gate[1] not in ("sigmoid", "silu"):
                 raise ValueError(f"output gate '{self.output_gate[1]}' is not known (sigmoid, silu)")
         self.output_scale = float(output_scale)
+        if self.output_scale != 1.0 and self.output_gate is None:
+            raise ValueError("a factor on the attention's result rides in the kernel of its output gate: it needs one")
         self.q_norm_weight = self.k_norm_weight = None
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
@@ -233,8 +235,6 @@ class GroupedQueryAttention(Mixer):
                                 fp32_weights=self.fp32_weights)
             if gate is not None:
                 ops.gate_mul(out, gate, out, self.output_gate[1], self.output_scale)
-            elif self.output_scale != 1.0:
-                raise NotImplementedError("a factor on the attention's result goes with an output gate")
             ops.gemm(out, self.o_weight, None, h, accumulate=accumulate)
             return
         table = self.position.rotary_table(qkv.device)
