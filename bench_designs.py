@@ -132,11 +132,11 @@ def sumevik_config(s: dict) -> dict:
     rec = {"type": "rglru", "mixer": {"width": W, "blocks": H, "conv": 4}}
     par = {"type": "parallel",
            "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": 1.0 / math.sqrt(d),
-                              "mask": {"size": WINDOW}, "rot": {"base": 1000000.0, "dims": d // 2}},
-                     "right": {"heads": H, "dim": d // 2, "vdim": d, "tau": 16.0}, "left_scale": 0.8, "right_scale": 1.1}}
+                              "mask": {"size": WINDOW}, "rot": {"base": 500000.0, "dims": d // 2}},
+                     "right": {"heads": H, "dim": d // 2, "vdim": d, "tau": 8.0}, "left_scale": 0.9, "right_scale": 1.2}}
     order = [rec, rec, par]
     layers = [dict(order[i % 3], mlp=moe if i % 2 else dense) for i in range(kugilix_runs(s))]
-    return {"architecture": "Sumevik", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "logit_scale": 0.5, "layers": layers}
+    return {"architecture": "Sumevik", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "logit_scale": 0.7, "layers": layers}
 
 
 def _timed(fn, flush, warmup=3, iters=5, reps=1):
@@ -588,7 +588,7 @@ def sumevik_kernel_numbers(s: dict, peaks: dict) -> dict:
         o = torch.empty(T, H * d, device=dev)
         ctx = ctx_of(q_lens, 0)
         t = _timed(lambda: ops.row_decay_recurrence(proj[:, :H * dk], proj[:, H * dk:2 * H * dk], proj[:, 2 * H * dk:2 * H * dk + H * d],
-                                                    z, 1.0 / 16.0, o, state, ctx, H, dk, d, q_scale=dk ** -0.5), flush)
+                                                    z, 1.0 / 8.0, o, state, ctx, H, dk, d, q_scale=dk ** -0.5), flush)
         moved = 2 * S * H * dk * d * 4 + T * (2 * H * dk + H * d) * 2 + T * H * dk * 4 + T * H * d * 4
         record(f"linear_attention_row_decay_{tag}", t, bytes_=moved, flops=4.0 * T * H * dk * d)
     # ---- the attention's own kernels: norm per head + rotation + cache write, the chunked attention with value heads of
@@ -617,7 +617,7 @@ def sumevik_kernel_numbers(s: dict, peaks: dict) -> dict:
         keys = sum((ctx_len + j) % WINDOW + 1 for j in range(q_len)) * batch
         record(f"chunk_attention_{name}", t, flops=4.0 * keys * H * d,
                bytes_=batch * G * (ctx_len % WINDOW + 1) * 2 * d * 2 + T * H * d * 4 if q_len == 1 else None)
-        t = _timed(lambda: ops.gate_mul(o, gate, o, "sigmoid", 0.8), flush, reps=reps)
+        t = _timed(lambda: ops.gate_mul(o, gate, o, "sigmoid", 0.9), flush, reps=reps)
         record(f"output_gate_{name}", t, bytes_=T * H * d * 6)
         og = torch.randn(T, H * d, device=dev)
         yy = torch.empty(T, H * d, dtype=bf, device=dev)

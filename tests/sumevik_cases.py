@@ -77,7 +77,7 @@ CASE_A = config([
     parallel_layer(attention(4, 2, 32, 48, chunk=48, rot=(16, 10000.0)), linear(2, 16, 32, 8.0),
                    experts(40, 6, 2, identity=2, groups=(4, 2), limit=0.7), scales=(0.7, 1.3)),
     recurrent_layer(64, 1, 2, experts(40, 6, 2, identity=2, groups=(4, 2), limit=0.7)),
-], width=64, logit_scale=0.5, ranks={1: 8})
+], width=64, logit_scale=0.6, ranks={1: 8})
 # B: what a usual model makes equal or one: a width that is no multiple of eight, a convolution of one tap (no inputs
 # kept), blocks of eight channels, one kv head, value heads of another size than the keys', whole heads rotating, a
 # chunk that is no multiple of a page, heads that are no multiple of 32, a decay root of one, one expert of five
@@ -260,6 +260,6 @@ def random_config(rng: random.Random) -> dict:
             right = linear(rng.choice([1, 2, 3, 4]), size(), size(), rng.choice([1.0, 4.0, 16.0]))
             ranks[i] = rng.choice([1, 4, 7, 16])
             layers.append(parallel_layer(left, right, feed_forward(),
-                                         scales=(rng.choice([1.0, 0.8, 1.5]), rng.choice([1.0, 1.1, 0.4]))))
+                                         scales=(rng.choice([1.0, 0.75, 1.5]), rng.choice([1.0, 1.25, 0.4]))))
     return config(layers, width=width, vocab=rng.randint(40, 200), eps=rng.choice([1e-6, 1e-5]),
                   logit_scale=rng.choice([None, 0.5, 2.0]), ranks=ranks)
