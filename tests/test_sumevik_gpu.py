@@ -250,6 +250,51 @@ def test_scan_carries_a_write_over_hundreds_of_tokens_and_several_requests(devic
     assert pos == 704 and torch.equal(torch.cat(rows), out[:704].cpu())
 
 
+def test_a_decay_close_to_one_is_never_rounded(device):
+    """Channels whose decay stays at 0.9999 to 0.999 for 4,000 tokens: what the first token wrote is left as exp(4,000 x
+    log a), to a few 1e-6 in 32-bit.  A decay formed as exp(log a) and rounded to 24 bits would be off by up to 3e-8 at
+    every step with the same sign, 1e-4 of the remembered value at the end.  The scan in one portion (tiles), in portions
+    and token by token; the linear attention's recurrence token after token, and as segments side by side."""
+    ops = _ops()
+    C, N = 96, 4000
+    log_a = -torch.logspace(-4, -3, C, dtype=F64)
+    want = torch.exp((N - 1) * log_a)  # the first token writes 1, the others only decay it
+    a = log_a.float().expand(N, C).contiguous().to(device)
+    b = torch.zeros(N, C, device=device)
+    b[0] = 1.0
+    exact = torch.exp((N - 1) * log_a.float().double())  # (the logarithms themselves are rounded once, to fp32)
+    for cuts in ([N], [1000, 7, 2000, 993], [3900] + [1] * 100):
+        state = torch.zeros(1, C, device=device)
+        pos = 0
+        for n in cuts:
+            out = torch.empty(n, C, device=device)
+            ops.rglru_scan(a[pos:pos + n], b[pos:pos + n], None, out, state, fake_ctx(device, [n], [pos], [0]), gelu=False)
+            pos += n
+        err = ((state[0].cpu().double() - exact) / exact).abs().max()
+        assert float(err) < 5e-6, (cuts[:2], float(err))
+    assert float(((exact - want) / want).abs().max()) < 1e-4  # what rounding the logarithms alone costs
+    # the linear attention: rows whose decay is sigmoid(z)^(1/16) with z from 5 to 9
+    d, dv = 32, 8
+    z = torch.linspace(5.0, 9.0, d, dtype=F64)
+    la = -torch.nn.functional.softplus(-z.float().double()) / 16.0
+    exact = torch.exp((N - 1) * la)
+    k = torch.zeros(N, d)
+    k[0] = 1.0
+    rows = torch.cat([torch.zeros(N, d), k, torch.ones(N, dv)], dim=1).to(device)
+    zz = z.float().expand(N, d).contiguous().to(device)
+    for segment, cuts in ((None, [250] * 16), (128, [N])):
+        state = torch.zeros(1, 1, dv, d, device=device)
+        pos = 0
+        for n in cuts:
+            r = rows[pos:pos + n]
+            out = torch.empty(n, dv, device=device)
+            ops.row_decay_recurrence(r[:, :d], r[:, d:2 * d], r[:, 2 * d:], zz[pos:pos + n], 1.0 / 16.0, out, state,
+                                     fake_ctx(device, [n], [pos], [0]), 1, d, dv, segment=segment)
+            pos += n
+        err = ((state[0, 0, 3].cpu().double() - exact) / exact).abs().max()
+        assert float(err) < 2e-5, (segment, float(err))
+
+
 def linear_weights(W, H, d, dv, rank, seed):
     g = torch.Generator().manual_seed(seed)
     r = lambda *s: torch.randn(*s, generator=g)
