@@ -252,7 +252,7 @@ def test_scan_carries_a_write_over_hundreds_of_tokens_and_several_requests(devic
 
 def test_a_decay_close_to_one_is_never_rounded(device):
     """Channels whose decay stays at 0.9999 to 0.999 for 4,000 tokens: what the first token wrote is left as exp(4,000 x
-    log a), to a few 1e-6 in 32-bit.  A decay formed as exp(log a) and rounded to 24 bits would be off by up to 3e-8 at
+    log a), to 1e-5 of itself in 32-bit.  A decay formed as exp(log a) and rounded to 24 bits would be off by up to 3e-8 at
     every step with the same sign, 1e-4 of the remembered value at the end.  The scan in one portion (tiles), in portions
     and token by token; the linear attention's recurrence token after token, and as segments side by side."""
     ops = _ops()
@@ -271,7 +271,7 @@ def test_a_decay_close_to_one_is_never_rounded(device):
             ops.rglru_scan(a[pos:pos + n], b[pos:pos + n], None, out, state, fake_ctx(device, [n], [pos], [0]), gelu=False)
             pos += n
         err = ((state[0].cpu().double() - exact) / exact).abs().max()
-        assert float(err) < 5e-6, (cuts[:2], float(err))
+        assert float(err) < 2e-5, (cuts[:2], float(err))
     assert float(((exact - want) / want).abs().max()) < 1e-4  # what rounding the logarithms alone costs
     # the linear attention: rows whose decay is sigmoid(z)^(1/16) with z from 5 to 9
     d, dv = 32, 8
