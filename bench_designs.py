@@ -569,6 +569,11 @@ def sumevik_kernel_numbers(s: dict, peaks: dict) -> dict:
         ctx = ctx_of(q_lens, 5)
         t = _timed(lambda: ops.rglru_gates(u, wa, wi, ba, bi, rate, a, b, 8.0), flush, reps=reps)
         record(f"recurrent_gates_{tag}", t, bytes_=2 * C * bs * 2 + T * C * (2 + 8), flops=2.0 * T * 2 * C * bs)
+        if T >= ops.RGLRU_TENSOR_CORE_MIN_TOKENS:  # the form a long bf16 step takes: the products on the tensor cores
+            stored = (wa.transpose(1, 2).contiguous(), wi.transpose(1, 2).contiguous())
+            t = _timed(lambda: ops.rglru_gates(u, wa, wi, ba, bi, rate, a, b, 8.0, stored=stored), flush, reps=reps)
+            record(f"recurrent_gates_tensor_cores_{tag}", t, bytes_=2 * C * bs * 2 + T * C * (2 + 8),
+                   tensor_flops=2.0 * T * 2 * C * bs)
         a.uniform_(-0.5, 0.0)  # (in case the gates left something else: the scan takes logarithms of decays)
         t = _timed(lambda: ops.rglru_scan(a, b, ybranch, y, state, ctx), flush, reps=reps)
         record(f"recurrent_scan_{tag}", t, bytes_=T * C * (8 + 2 + 2) + 2 * S * C * 4)

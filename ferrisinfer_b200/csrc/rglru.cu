@@ -26,6 +26,7 @@
 // for a channel reads the channel's state, moves it on and writes the gated output, so a and b never reach memory and
 // the scan is no launch of its own.
 #include <math.h>
+#include <mma.h>
 
 #include "common.cuh"
 
@@ -36,7 +37,6 @@ constexpr int RG_TOKENS = 8, RG_COLS = 64, RG_PARTS = 4, RG_THREADS = RG_COLS * 
 // channels fills the SMs, and a tile of 256 tokens costs a chain of 8 + 32 + 8 steps
 constexpr int SCAN_CH = 8, SCAN_SEGS = 32, SCAN_SEG_TOKENS = 8, SCAN_THREADS = SCAN_CH * SCAN_SEGS;
 
-__device__ __forceinline__ float softplus_r(float v) { return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v))); }
 __device__ __forceinline__ float sigmoid_r(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float gelu_tanh_r(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -122,6 +122,71 @@ __global__ void __launch_bounds__(RG_THREADS) rglru_gates_kernel(const T* u, int
             const size_t at = (size_t)(t0 + r) * C + c;
             a_out[at] = log_a, b_out[at] = b;
         }
+    }
+}
+
+// The gates of a long step in bf16 on the tensor cores: a block takes 64 tokens x 64 outputs of one gate block for both
+// gates; the tokens' inputs of the gate block stand in shared memory (they are also the u of the epilogue), the weights
+// are read as they are stored ([block][output][input] is the column-major B operand), sums are fp32 fragments that pass
+// through shared memory to the same epilogue as above.  bs a multiple of 64.
+constexpr int TG_M = 64, TG_N = 64, TG_THREADS = 128;
+__global__ void __launch_bounds__(TG_THREADS) rglru_gates_mma_kernel(const bf16* u, int ldu, const bf16* __restrict__ wa,
+                                                                     const bf16* __restrict__ wi,
+                                                                     const float* __restrict__ ba,
+                                                                     const float* __restrict__ bi,
+                                                                     const float* __restrict__ sp, float* __restrict__ a_out,
+                                                                     float* __restrict__ b_out, int tokens, int C, int bs,
+                                                                     float decay_factor) {
+    using namespace nvcuda;
+    extern __shared__ __align__(32) uint8_t tg_smem[];
+    const int lda = bs + 8;  // elements: sixteen rows (a fragment) are a multiple of 32 bytes, eight rows meet eight bank groups
+    bf16* A = reinterpret_cast<bf16*>(tg_smem);
+    float* Z = reinterpret_cast<float*>(tg_smem + (((size_t)TG_M * lda * sizeof(bf16) + 31) & ~(size_t)31));  // [2][TG_M][TG_N]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t0 = blockIdx.x * TG_M, blk = blockIdx.y, n0 = blockIdx.z * TG_N;
+    const int warp = threadIdx.x >> 5;
+    const int chunks = bs >> 3;  // 16-byte pieces of a row
+    for (int i = threadIdx.x; i < TG_M * chunks; i += TG_THREADS) {
+        const int r = i / chunks, c8 = (i - r * chunks) << 3;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (t0 + r < tokens) v = *reinterpret_cast<const uint4*>(u + (size_t)(t0 + r) * ldu + (size_t)blk * bs + c8);
+        *reinterpret_cast<uint4*>(A + (size_t)r * lda + c8) = v;
+    }
+    __syncthreads();
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc_a[TG_N / 16], acc_i[TG_N / 16];
+#pragma unroll
+    for (int j = 0; j < TG_N / 16; ++j) wmma::fill_fragment(acc_a[j], 0.0f), wmma::fill_fragment(acc_i[j], 0.0f);
+    const bf16* pa = wa + ((size_t)blk * bs + n0) * bs;
+    const bf16* pi = wi + ((size_t)blk * bs + n0) * bs;
+#pragma unroll 2
+    for (int k0 = 0; k0 < bs; k0 += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+        wmma::load_matrix_sync(fa, A + (size_t)(16 * warp) * lda + k0, lda);
+#pragma unroll
+        for (int j = 0; j < TG_N / 16; ++j) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+            wmma::load_matrix_sync(fb, pa + (size_t)(16 * j) * bs + k0, bs);
+            wmma::mma_sync(acc_a[j], fa, fb, acc_a[j]);
+            wmma::load_matrix_sync(fb, pi + (size_t)(16 * j) * bs + k0, bs);
+            wmma::mma_sync(acc_i[j], fa, fb, acc_i[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < TG_N / 16; ++j) {
+        wmma::store_matrix_sync(Z + (size_t)(16 * warp) * TG_N + 16 * j, acc_a[j], TG_N, wmma::mem_row_major);
+        wmma::store_matrix_sync(Z + (size_t)(TG_M + 16 * warp) * TG_N + 16 * j, acc_i[j], TG_N, wmma::mem_row_major);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < TG_M * TG_N; i += TG_THREADS) {
+        const int r = i / TG_N, n = i - r * TG_N;
+        if (t0 + r >= tokens) break;
+        const int c = blk * bs + n0 + n;
+        const float log_a = -decay_factor * sp[c] * sigmoid_r(Z[(size_t)r * TG_N + n] + ba[c]);
+        const float gate = sigmoid_r(Z[(size_t)(TG_M + r) * TG_N + n] + bi[c]);
+        const size_t at = (size_t)(t0 + r) * C + c;
+        a_out[at] = log_a;
+        b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gate * to_float(A[(size_t)r * lda + n0 + n]);
     }
 }
 
@@ -215,6 +280,27 @@ __global__ void __launch_bounds__(256) rglru_scan_single_kernel(const float* a, 
 // [tokens, C]; decay_factor: the constant c of log a = -c r softplus(lam).  With `state` (fp32 [slots, C]; a step in
 // which request t brings row t alone): a_out and b_out are not written; the state of slot seq_state_slot[t] moves on
 // (if write_state) and out[t] = s * act(y[t]) as in ferris_rglru_scan.
+// The tensor-core form of the gates (a long step in bf16, not a step of single tokens): wa, wi as the folder stores them,
+// [blocks, output, input]; C / blocks a multiple of 64, rows of u and the matrices on 32 bytes.  Returns
+// FERRIS_BAD_ARGUMENT (and says why) for what it does not take.
+FERRIS_API int ferris_rglru_gates_mma(const void* u, int ldu, const void* wa, const void* wi, const float* ba,
+                                      const float* bi, const float* sp, float* a_out, float* b_out, int tokens, int C,
+                                      int blocks, float decay_factor, void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (C <= 0 || blocks <= 0 || C % blocks || blocks > 65535) FERRIS_REFUSE("recurrent unit gates: %d channels in %d blocks", C, blocks);
+    const int bs = C / blocks;
+    if (bs % TG_N || (ldu & 7) || (((uintptr_t)u | (uintptr_t)wa | (uintptr_t)wi) & 31) || !a_out || !b_out)
+        FERRIS_REFUSE("recurrent unit gates on tensor cores: blocks of %d channels (a multiple of %d), rows on 32 bytes", bs, TG_N);
+    const size_t smem = (((size_t)TG_M * (bs + 8) * sizeof(bf16) + 31) & ~(size_t)31) + (size_t)2 * TG_M * TG_N * sizeof(float);
+    if (smem > 200 * 1024) FERRIS_REFUSE("recurrent unit gates on tensor cores: blocks of %d channels are more than shared memory holds", bs);
+    int e_ = ferris_allow_dynamic_smem((const void*)rglru_gates_mma_kernel, smem);
+    if (e_ != FERRIS_OK) return e_;
+    ferris_launch(rglru_gates_mma_kernel, dim3((tokens + TG_M - 1) / TG_M, blocks, bs / TG_N), dim3(TG_THREADS), smem,
+                  (cudaStream_t)stream, (const bf16*)u, ldu, (const bf16*)wa, (const bf16*)wi, ba, bi, sp, a_out, b_out, tokens, C,
+                  bs, decay_factor);
+    FERRIS_LAUNCH_CHECK();
+}
+
 FERRIS_API int ferris_rglru_gates(const void* u, int ldu, int dtype, const void* wa, const void* wi, const float* ba,
                                   const float* bi, const float* sp, float* a_out, float* b_out, int tokens, int C,
                                   int blocks, float decay_factor, float* state, const int* seq_state_slot, const void* y,

@@ -1231,16 +1231,21 @@ def row_decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_
     )
 
 
+RGLRU_TENSOR_CORE_MIN_TOKENS = 256  # from here on a bf16 step forms the gates' products on the tensor cores (at 64 tokens the CUDA-core form takes 16 us, this one 22)
+
+
 def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
                 softplus_lam: torch.Tensor, a_out: Optional[torch.Tensor], b_out: Optional[torch.Tensor], decay_factor: float,
-                step: Optional[tuple] = None):
+                step: Optional[tuple] = None, stored: Optional[tuple] = None):
     """The gates of a gated linear recurrent unit: per block n of the channels r = sigmoid(Ra[n] u_n + ba),
     i = sigmoid(Ri[n] u_n + bi); log a = -decay_factor r softplus_lam; b = sqrt(1 - a^2) i u.  ``wa_t``, ``wi_t``:
     [blocks, in, out] (the matrices transposed) in u's type; ba, bi, softplus_lam fp32 [C]; a_out (which receives log a,
     not a: the scan never rounds a decay close to one to 24 bits) and b_out fp32 [T, C].
     ``step`` = (state fp32 [slots, C], ctx, y or None, out, gelu, write_state) for a step in which every request brings
     one token: the kernel moves the state on itself and writes out = s * act(y) (see ``rglru_scan``); a_out and b_out
-    are then not needed."""
+    are then not needed.  ``stored`` = (Ra, Ri) as the folder stores them ([blocks, out, in]): a bf16 step of at least
+    RGLRU_TENSOR_CORE_MIN_TOKENS tokens with gate blocks of a multiple of 64 channels then forms the two products on the
+    tensor cores (bf16 operands, fp32 sums; the same epilogue)."""
     T, C, ldu = _rows(u, "recurrent unit input")
     _need(wa_t, "recurrence gate matrices", u.dtype)
     _need(wi_t, "input gate matrices", u.dtype)
@@ -1248,6 +1253,20 @@ def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: tor
     bs = C // max(blocks, 1)
     for t_, name in ((ba, "recurrence gate bias"), (bi, "input gate bias"), (softplus_lam, "decay rates")):
         _need(t_, name, torch.float32)
+    if (stored is not None and step is None and u.dtype == torch.bfloat16 and T >= RGLRU_TENSOR_CORE_MIN_TOKENS
+            and bs % 64 == 0 and ldu % 8 == 0 and u.data_ptr() % 32 == 0):
+        wa, wi = stored
+        _need(wa, "recurrence gate matrices", u.dtype)
+        _need(wi, "input gate matrices", u.dtype)
+        _need(a_out, "decays", torch.float32)
+        _need(b_out, "gated inputs", torch.float32)
+        if (wa.shape != (blocks, bs, bs) or wi.shape != wa.shape or ba.numel() != C or bi.numel() != C
+                or softplus_lam.numel() != C or a_out.shape != (T, C) or b_out.shape != (T, C)):
+            raise KernelError(f"recurrent unit gates: u {tuple(u.shape)}, matrices {tuple(wa.shape)}")
+        _check(_lib().ferris_rglru_gates_mma(_ptr(u), _c_int(ldu), _ptr(wa), _ptr(wi), _ptr(ba), _ptr(bi), _ptr(softplus_lam),
+                                             _ptr(a_out), _ptr(b_out), _c_int(T), _c_int(C), _c_int(blocks),
+                                             _c_float(decay_factor), _stream()), "recurrent unit gates (tensor cores)")
+        return
     state = slots = y = out = None
     ldy = ldo = 0
     gelu = write_state = False

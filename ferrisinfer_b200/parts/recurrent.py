@@ -226,8 +226,9 @@ class GatedLinearUnit(Mixer):
         self.in_bias = torch.cat([bias, bias.new_zeros(pad)]).contiguous() if pad else bias.contiguous()
         self.conv_weight, self.conv_bias = tensors[f"{prefix}.{n['conv']}"], tensors[f"{prefix}.{n['conv']}.b"]
         # the gates' matrices transposed ([block, in, out]): the threads of the gates kernel read consecutive weights
-        self.ra_t = tensors.pop(f"{prefix}.{n['ra']}").transpose(1, 2).contiguous()
-        self.ri_t = tensors.pop(f"{prefix}.{n['ri']}").transpose(1, 2).contiguous()
+        # (and as they are stored, for the tensor-core form of long bf16 steps, whose B operand that layout is)
+        self.ra, self.ri = tensors.pop(f"{prefix}.{n['ra']}").contiguous(), tensors.pop(f"{prefix}.{n['ri']}").contiguous()
+        self.ra_t, self.ri_t = self.ra.transpose(1, 2).contiguous(), self.ri.transpose(1, 2).contiguous()
         self.ra_bias = tensors[f"{prefix}.{n['ra']}.b"].reshape(-1).contiguous()
         self.ri_bias = tensors[f"{prefix}.{n['ri']}.b"].reshape(-1).contiguous()
         # softplus of the decay's parameter, formed once in 64-bit and rounded once
@@ -255,7 +256,8 @@ class GatedLinearUnit(Mixer):
                             step=(state.state, ctx, proj[:, :C], y, gelu, owns_cache))
         else:
             a, b = ws.get("recurrent_unit_a", (T, C), torch.float32), ws.get("recurrent_unit_b", (T, C), torch.float32)
-            ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, a, b, self.decay_factor)
+            ops.rglru_gates(u, self.ra_t, self.ri_t, self.ra_bias, self.ri_bias, self.rate, a, b, self.decay_factor,
+                            stored=(self.ra, self.ri))
             ops.rglru_scan(a, b, proj[:, :C], y, state.state, ctx, gelu=gelu, write_state=owns_cache)
         ops.gemm(y, self.o_weight, None, h, accumulate=accumulate)
 

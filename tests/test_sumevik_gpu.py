@@ -212,6 +212,34 @@ def test_recurrent_unit_whole_in_portions_and_token_by_token(device, C, blocks, 
             assert torch.allclose(state[2].cpu().double(), last, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("T,C,blocks", [(256, 64, 1), (300, 256, 2), (461, 384, 3), (1000, 128, 2)])
+def test_gates_on_tensor_cores_against_the_plain_gates(device, T, C, blocks):
+    """Long bf16 steps with gate blocks of a multiple of 64 channels: log a and the gated input from the tensor-core form
+    (weights as stored) against the plain formulas and against the CUDA-core form (weights transposed)."""
+    ops = _ops()
+    torch.manual_seed(T + C)
+    bs = C // blocks
+    u = torch.randn(T, C).to(BF16)
+    ra, ri = (2.0 * torch.randn(blocks, bs, bs) / math.sqrt(bs)).to(BF16), (2.0 * torch.randn(blocks, bs, bs) / math.sqrt(bs)).to(BF16)
+    ba, bi, lam = 0.2 * torch.randn(C), 0.2 * torch.randn(C), -6.0 + 5.0 * torch.rand(C)
+    rate = torch.nn.functional.softplus(lam.double()).float()
+    ub = u.double().reshape(T, blocks, bs)
+    r = torch.sigmoid(torch.einsum("tnk,nok->tno", ub, ra.double()).reshape(T, C) + ba.double())
+    i = torch.sigmoid(torch.einsum("tnk,nok->tno", ub, ri.double()).reshape(T, C) + bi.double())
+    log_a = -8.0 * r * rate.double()
+    want_b = torch.sqrt(1.0 - torch.exp(2.0 * log_a)) * i * u.double()
+    dev = lambda t: t.to(device)
+    outs = []
+    for stored in (None, (dev(ra), dev(ri))):
+        a, b = torch.empty(T, C, device=device), torch.empty(T, C, device=device)
+        ops.rglru_gates(dev(u), dev(ra.transpose(1, 2).contiguous()), dev(ri.transpose(1, 2).contiguous()), dev(ba), dev(bi),
+                        dev(rate), a, b, 8.0, stored=stored)
+        assert torch.allclose(a.cpu().double(), log_a, atol=1e-5, rtol=1e-4), stored is None
+        assert torch.allclose(b.cpu().double(), want_b, atol=1e-5, rtol=1e-4), stored is None
+        outs.append((a, b))
+    assert ops.RGLRU_TENSOR_CORE_MIN_TOKENS <= T  # the second pass ran the tensor-core kernel
+
+
 def test_scan_carries_a_write_over_hundreds_of_tokens_and_several_requests(device):
     """A decay of one (a logarithm of zero) everywhere but where a token writes: what token 3 wrote is read 700 tokens later, through tiles of
     the scan, portions that end in the middle of a tile and single tokens; three requests of unequal length in one
