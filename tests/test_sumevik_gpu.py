@@ -804,14 +804,16 @@ def test_a_slot_that_is_used_again_starts_from_zero(device):
     check_rows(got, rows_of(case, names), "float32", "a slot used again")
 
 
-@pytest.mark.parametrize("case", ["A", "D"])
-def test_a_long_prompt_and_its_decoded_tail(device, case):
-    """520 tokens, the last 40 one by one, in 32-bit: every position against the plain implementation, so that states
-    carried over hundreds of tokens and several chunks are in every logit that is compared."""
+@pytest.mark.parametrize("case,dtype", [("A", "float32"), ("D", "float32"), ("A", "bfloat16")])
+def test_a_long_prompt_and_its_decoded_tail(device, case, dtype):
+    """520 tokens, the last 40 one by one: every position against the plain implementation, so that states carried
+    over hundreds of tokens and several chunks are in every logit that is compared.  In bfloat16 the portion of 480
+    tokens also runs the forms of long steps (the gates of the block of 64 channels on the tensor cores, the linear
+    attention's segments side by side, the sorted experts)."""
     ids, want = wanted(case, 520, 77)
-    runner = make_runner(cases.CASES[case], weights_of(case), "float32", device, num_pages=48)
+    runner = make_runner(cases.CASES[case], weights_of(case), dtype, device, num_pages=48)
     got = helpers.replay(runner, helpers.trace_tail_decoded({"far": ids}, tail=40))
-    check_rows(got, {"far": want}, "float32", "a long prompt and its tail")
+    check_rows(got, {"far": want}, dtype, "a long prompt and its tail")
 
 
 MID = cases.config([
