@@ -1,4 +1,4 @@
-// A gated linear recurrent unit over channels (the recurrence of a Griffin-style recurrent block):
+// A gated linear recurrence per channel (the recurrence inside a recurrent block in the manner of Griffin):
 //
 //   per block n of the channels (C / blocks neighbouring channels):  r = sigmoid(Ra[n] u_n + ra_n),  i = sigmoid(Ri[n] u_n + ri_n)
 //   log a = -c * r * softplus(lam);   a = exp(log a);   s_t = a s_(t-1) + sqrt(1 - a^2) * i * u_t;   out_t = s_t * act(y_t)

@@ -13,7 +13,7 @@
     S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
   h += (rmsnorm_in_groups(o * SiLU(z)) * n) Wo^T       the gate before the norm, ``norm_groups`` equal parts.
 
-``GatedLinearUnit`` (the recurrent block of a Griffin-style model, with a real-gated linear recurrent unit):
+``GatedLinearUnit`` (a recurrent block in the manner of Griffin: a linear recurrence per channel whose two gates are real numbers):
   b = a(y Wy^T + by), a the tanh form of GELU;  u = conv(y Wx^T + bx) + cb, a short causal convolution per channel, no
   activation;  per block n of the C channels (C / blocks neighbours): r = sigmoid(Ra[n] u_n + ra), i = sigmoid(Ri[n] u_n + ri);
     log a = -decay_factor r softplus(lam);  s_t = exp(log a) s_(t-1) + sqrt(1 - exp(2 log a)) i u_t
